@@ -40,15 +40,64 @@ enum fq3c_kind {
                          rows (buffer address, hist rows, new rows, cols, ld): rows [new, new + hist) of each bf16 buffer
                          move to [0, hist) (overlapping ranges in batches of `new` rows, a block barrier between them);
                          then *(int32*)C += i0.  Replaces 2 x FQ3C_COPY per buffer (through scratch) + FQ3C_ADVANCE    */
-  FQ3C_QKNORM_ROPE_KV = 8 /* dense talker prefill: A = fused qkv rows [M, lda], i0 q heads, i1 kv heads of dim 128; q/k heads get the
+  FQ3C_QKNORM_ROPE_KV = 8, /* dense talker prefill: A = fused qkv rows [M, lda], i0 q heads, i1 kv heads of dim 128; q/k heads get the
                              per-head RMSNorm (bf16 gamma p0 / p1, eps f0) and the rotary embedding from the bf16 tables B (cos) /
                              bias (sin) at position row + i2, in place; finished k / v rows also go to the static KV cache
                              C (K) / C2 (V), each [kv_head][ldc][128] (talker_graph.py:153-170 without the copy)            */
+  /* ---- sequence-model ops (ABI 6): decoder-only language models lowered to op lists with a 32-bit residual stream.
+   * Unless said otherwise A is f32 [M, lda], the output is bf16 or, with FQ3C_OUT_F32, f32; weights (B) are bf16 or, with
+   * FQ3C_F32, f32.  Per-sequence state lives in caller-owned buffers; the position counter is a device int32 (p0) so that a
+   * captured list replays at any position. */
+  FQ3C_EMBED = 12,    /* C f32 [M, N] = B[ids[m], :]; A = device int32 ids [M]                                                */
+  FQ3C_TCONV = 13,    /* causal per-channel convolution over time with carried inputs: C[m, c] = (RESID ? A[m, c] : 0) + bias[c] +
+                         sum_j B(f32 [N, taps])[c, j] * in[m - (taps - 1) + j, c], where rows before this call come from the history
+                         p0 (f32 [taps - 1, N], oldest first; zeros at a sequence's start).  The next history (the last taps - 1
+                         inputs) is written to p1 (f32 [taps - 1, N]); FQ3C_COMMIT installs it.                                */
+  FQ3C_GNORM = 14,    /* RMS norm in i0 equal consecutive groups, eps f0, times scale (f32 [N]); RESID: C = res (f32 [M, ldr]) +
+                         that (res may be C).  C2, when given: the bf16 rounding of the same result.  p0, when given (device int32):
+                         output row m is row *p0 + m of C (cache append)                                                       */
+  FQ3C_BDGEMM = 15,   /* block-diagonal product: i0 blocks of [i2 out, cin in]; C[m, b * i2 + n] = epi(sum_k A[m, (b % i1) * cin + k] *
+                         B[b][n][k] + bias[b * i2 + n]); N = i0 * i2.  Flags: BIAS, SIGMOID, OUT_F32, F32 (B is f32)              */
+  FQ3C_LATENT_ATTN = 16, /* attention over a cache of shared latent rows in absorbed form: A = queries already projected into latent
+                         space f32 [M, i0 heads * i1 rank]; B = latent cache [>= *p0 + M rows, ldr] (bf16, F32: f32); query m sees
+                         rows [0, *p0 + m]; score = f0 * (q . c); softmax whose denominator also holds exp(scale[h]) (a per-head sink
+                         without key or value; scale = f32 [i0], may be NULL); C f32 [M, i0 * i1] = sum_j p_j c_j.  i2 = heads per
+                         block; K = key-range splits (> 1: ws holds the partial states and a second launch merges them)           */
+  FQ3C_LRU_SCAN = 17, /* gated diagonal linear recurrence, 32-bit state: per channel c and row t, with gates g = A f32 [M, lda]
+                         (recurrence gate r at column c, input gate i at column N + c, already sigmoid), input u = B f32 [M, cin],
+                         branch y = res f32 [M, ldr] (before its activation), lam = scale f32 [N]:
+                         a = exp(-f0 * r * softplus(lam)),  S <- a S + sqrt(1 - a^2) * i * u,  C[t, c] = S * gelu_tanh(y).
+                         The state is read from p0 (f32 [N]) and the next state written to C2 (f32 [N]; FQ3C_COMMIT installs it).
+                         Long runs of rows are cut into pieces that fold in parallel (ws = f32 [2 * pieces * N])                */
+  FQ3C_POLYNORM = 18, /* C[m, :] = p0[0] n(z) + p0[1] n(z^2) + p0[2] n(z^3) + p0[3], z = A[m, :N], n(v) = v / sqrt(mean(v^2) + f0),
+                         powers element by element; p0 = f32 [4] on the device                                                 */
+  FQ3C_ROUTER = 19,   /* mixture-of-experts router: A = f32 logits [M, N]; s = softmax over N; choice = s + bias (f32 [N], may be
+                         NULL); experts form i1 equal groups of neighbours, a group's score is its largest choice, only the best i2
+                         groups stay eligible; the i0 largest eligible choices are taken (lower index wins a tie);
+                         weights = s[chosen] / (sum + 1e-20) * f0.  C = int32 [M, i0] expert ids, C2 = f32 [M, i0] weights        */
+  FQ3C_MOE_SORT = 20, /* A = int32 ids [M, i0]; experts with id < i1 are real.  C = int32 [i1 + 1] segment starts, C2 = int32
+                         [M * i0] token of each sorted position, ws = int32 [M * i0] sorted position of (m, j) or -1 (not real);
+                         positions of one expert are in token order                                                            */
+  FQ3C_GGEMM = 21,    /* grouped product over sorted rows: for expert e and positions p in [seg[e], seg[e + 1]):
+                         C[p, :N] = epi(sum_k A[rows ? rows[p] : p, k] * B[e][n][k]); seg = p0 (int32 [i0 + 1]), rows = p1 (int32) or
+                         NULL, i0 experts, M = upper bound of positions.  A bf16, or f32 with FQ3C_A_F32; B bf16, F32: both f32     */
+  FQ3C_MOE_COMBINE = 22, /* C f32 [M, N] = sum_j w[m, j] * (ids[m, j] >= i1 ? x[m, :] : Y[pos[m, j], :]) (+ res[m, :]);
+                         A = Y f32, B = x f32 [M, ldr] (identity experts), p0 = ids int32 [M, i0], p1 = w f32 [M, i0],
+                         ws = pos int32 [M, i0], res = f32 [M, ldr] or NULL (shared expert)                                      */
+  FQ3C_COMMIT = 23    /* end of a step: A = device int64 [M, 3] rows (dst, src, bytes), bytes a multiple of 4, copied in one launch;
+                         then *(int32*)C += i0 (the sequence's position counter)                                               */
 };
 
 enum fq3c_flags {
   FQ3C_BIAS = 1, FQ3C_GELU = 2, FQ3C_RESID = 4, FQ3C_SCALE = 8, FQ3C_SWIGLU = 16, FQ3C_CLAMP = 32,
-  FQ3C_OUT_F32 = 64, FQ3C_SNAKE2 = 128 /* also write C2 = snake(C) */, FQ3C_SILU = 256 /* text_projection: Linear -> SiLU */
+  FQ3C_OUT_F32 = 64, FQ3C_SNAKE2 = 128 /* also write C2 = snake(C) */, FQ3C_SILU = 256 /* text_projection: Linear -> SiLU */,
+  /* ABI 6 */
+  FQ3C_F32 = 512        /* GEMM / BDGEMM / GGEMM / EMBED / LATENT_ATTN: the weights (cache) are f32 and the product is true 32-bit;
+                           for FQ3C_GEMM this means A is f32 too, bias / erf-GELU / tanh-GELU / OUT_F32 are the only epilogues */,
+  FQ3C_NOROUND = 1024   /* GEMM with OUT_F32: the accumulator is not rounded to bf16 on its way out */,
+  FQ3C_GELU_TANH = 2048 /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */,
+  FQ3C_SIGMOID = 4096,
+  FQ3C_A_F32 = 8192     /* GGEMM: A rows are f32 while B is bf16 */
 };
 
 typedef struct fq3c_op {

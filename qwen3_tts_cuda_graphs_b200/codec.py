@@ -31,7 +31,10 @@ from .config import CodecDecoderConfig
 
 K_GEMM, K_RVQ, K_RMSNORM, K_ROPE, K_ATTN, K_DWCONV, K_LAYERNORM, K_SNAKE = range(8)
 K_COPY, K_ADVANCE, K_ROLL = 9, 10, 11
+(K_EMBED, K_TCONV, K_GNORM, K_BDGEMM, K_LATENT_ATTN, K_LRU_SCAN, K_POLYNORM, K_ROUTER, K_MOE_SORT, K_GGEMM, K_MOE_COMBINE,
+ K_COMMIT) = range(12, 24)
 F_BIAS, F_GELU, F_RESID, F_SCALE, F_SWIGLU, F_CLAMP, F_OUT_F32, F_SNAKE2, F_SILU = 1, 2, 4, 8, 16, 32, 64, 128, 256
+F_F32, F_NOROUND, F_GELU_TANH, F_SIGMOID, F_A_F32 = 512, 1024, 2048, 4096, 8192
 
 
 class Op(C.Structure):
@@ -141,7 +144,7 @@ def load_lib():
     lib.fq3c_graph_launch.argtypes = [C.c_void_p, C.c_void_p]
     lib.fq3c_graph_destroy.restype = C.c_int
     lib.fq3c_graph_destroy.argtypes = [C.c_void_p]
-    if lib.fq3c_abi_version() != 5:
+    if lib.fq3c_abi_version() != 6:
         raise CodecError("libfq3codec.so ABI version mismatch")
     _lib = lib
     return lib
@@ -247,6 +250,27 @@ class _Plan:
         self.runs = 0
         self.graph = None          # fq3c_graph handle once the plan has been captured
         self.graph_failed = False
+
+
+def run_op_plan(lib, plan: _Plan, use_graphs: bool = True):
+    """Launch a plan's op list on the current stream; from its second use on a plan replays as one CUDA graph (its launches are
+    static: same ops, same buffers).  Shared by the codec decoder and the sequence-model engine."""
+    if plan.arr is None:
+        plan.arr = (Op * len(plan.ops))(*plan.ops)
+    stream = torch.cuda.current_stream().cuda_stream
+    if use_graphs and plan.runs >= 1 and getattr(plan, "graph", None) is None and not plan.graph_failed:
+        h = C.c_void_p()
+        if lib.fq3c_graph_create(plan.arr, len(plan.ops), C.byref(h)) == 0:
+            plan.graph = h
+        else:
+            plan.graph_failed = True
+    plan.runs += 1
+    if getattr(plan, "graph", None) is not None:
+        rc = lib.fq3c_graph_launch(plan.graph, stream)
+    else:
+        rc = lib.fq3c_run(plan.arr, len(plan.ops), stream)
+    if rc != 0:
+        raise CodecError(lib.fq3c_last_error().decode())
 
 
 class CodecDecoder:
@@ -474,23 +498,7 @@ class CodecDecoder:
 
     def run_plan(self, plan: _Plan):
         """Launch a plan's op list on the current stream (also the hook the per-op parity tests use)."""
-        if plan.arr is None:
-            plan.arr = (Op * len(plan.ops))(*plan.ops)
-        stream = torch.cuda.current_stream().cuda_stream
-        if self.use_graphs and plan.runs >= 1 and getattr(plan, "graph", None) is None and not plan.graph_failed:
-            # second use of a cached plan: its launches are static, replay them as one CUDA graph from now on
-            h = C.c_void_p()
-            if self.lib.fq3c_graph_create(plan.arr, len(plan.ops), C.byref(h)) == 0:
-                plan.graph = h
-            else:
-                plan.graph_failed = True
-        plan.runs += 1
-        if getattr(plan, "graph", None) is not None:
-            rc = self.lib.fq3c_graph_launch(plan.graph, stream)
-        else:
-            rc = self.lib.fq3c_run(plan.arr, len(plan.ops), stream)
-        if rc != 0:
-            raise CodecError(self.lib.fq3c_last_error().decode())
+        run_op_plan(self.lib, plan, self.use_graphs)
 
     def n_samples(self, T: int) -> int:
         return self.cfg.n_samples(T)

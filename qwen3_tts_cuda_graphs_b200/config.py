@@ -233,3 +233,113 @@ def with_layers(cfg: TTSConfig, talker_layers: int, predictor_layers: Optional[i
     t = replace(cfg.talker, num_hidden_layers=talker_layers)
     p = cfg.predictor if predictor_layers is None else replace(cfg.predictor, num_hidden_layers=predictor_layers)
     return replace(cfg, talker=t, predictor=p)
+
+
+# ------------------------------------------------------------------------------------------------
+# Sequence models (decoder-only language models run by seq_engine.SequenceEngine on the op-list library)
+# ------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class LatentAttentionConfig:
+    """Attention whose keys and values are up-projections of one shared low-rank latent per position (only the latent is
+    cached), without positional rotation, with a learned per-head sink in the softmax denominator."""
+
+    heads: int
+    dim: int        # query / key size per head
+    vdim: int       # value size per head
+    kv_rank: int    # latent size
+    scale: float    # multiplies q . k
+
+
+@dataclass(frozen=True)
+class RglruConfig:
+    """Recurrent block with a real-gated diagonal linear recurrence: a gelu branch times a conv -> gated-recurrence branch."""
+
+    width: int
+    blocks: int     # the two gates are block-diagonal with this many square blocks
+    conv: int       # taps of the causal per-channel convolution in front of the recurrence
+    decay: float = 8.0   # log a = -decay * r * softplus(lam); fixed by the design
+
+
+@dataclass(frozen=True)
+class DenseFFConfig:
+    ff: int
+
+
+@dataclass(frozen=True)
+class MoEFFConfig:
+    experts: int        # real experts (with tensors)
+    identity: int       # trailing router outputs whose "expert" returns its input
+    top: int
+    groups: int         # router outputs (real + identity) form this many equal groups of neighbours
+    keep: int           # only the best `keep` groups stay eligible
+    scale: float        # multiplies the normalised weights
+    expert_ff: int
+    shared_ff: int      # 0: no shared expert
+
+    @property
+    def routed(self) -> int:
+        return self.experts + self.identity
+
+
+@dataclass(frozen=True)
+class SeqLayerConfig:
+    type: str                       # "latent_attention" | "rglru"
+    mixer: object
+    mlp: Optional[object]           # DenseFFConfig | MoEFFConfig | None
+
+
+@dataclass(frozen=True)
+class SidalornConfig:
+    """Sidalorn: post-sublayer grouped RMS norms (x += norm(sublayer(x))), a causal per-channel convolution in front of every
+    mixer, latent-attention and RG-LRU mixers in a configured order, PolyNorm dense or grouped-router MoE feed-forwards."""
+
+    architecture = "Sidalorn"
+    vocab: int
+    width: int
+    norm_eps: float
+    norm_groups: int
+    canon_taps: int                 # 0: no input convolution
+    layers: Tuple[SeqLayerConfig, ...]
+
+    @staticmethod
+    def from_dict(raw: dict) -> "SidalornConfig":
+        norm = raw.get("norm") or {}
+        canon = raw.get("canon") or {}
+        layers = []
+        for L in raw["layers"]:
+            m = L["mixer"]
+            if L["type"] == "latent_attention":
+                mixer = LatentAttentionConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), int(m["kv_rank"]), float(m["scale"]))
+            elif L["type"] == "rglru":
+                mixer = RglruConfig(int(m["width"]), int(m["blocks"]), int(m["conv"]))
+            else:
+                raise ValueError(f"unknown mixer type {L['type']!r}")
+            f = L.get("mlp")
+            if f is None:
+                mlp = None
+            elif f["kind"] == "dense":
+                mlp = DenseFFConfig(int(f["ff"]))
+            elif f["kind"] == "moe":
+                r = f["router"]
+                g = r.get("groups") or {}
+                sh = f.get("shared")
+                mlp = MoEFFConfig(int(r["experts"]), int(r.get("identity", 0)), int(r["top"]), int(g.get("count", 1)), int(g.get("keep", g.get("count", 1))),
+                                  float(r.get("scale", 1.0)), int(f["expert"]["ff"]), int(sh["ff"]) if sh else 0)
+            else:
+                raise ValueError(f"unknown feed-forward kind {f['kind']!r}")
+            layers.append(SeqLayerConfig(L["type"], mixer, mlp))
+        return SidalornConfig(int(raw["vocab"]), int(raw["width"]), float(norm.get("eps", 1e-6)), int(norm.get("groups", 1)),
+                              int(canon.get("taps", 0)), tuple(layers))
+
+
+# config.json "architecture" -> (config class, "module:class" of the model that lowers it to op lists)
+SEQUENCE_ARCHITECTURES = {
+    "Sidalorn": (SidalornConfig, "sidalorn:SidalornModel"),
+}
+
+
+def sequence_config_from_dict(raw: dict):
+    arch = raw.get("architecture")
+    if arch not in SEQUENCE_ARCHITECTURES:
+        raise ValueError(f"unknown sequence-model architecture {arch!r} (known: {sorted(SEQUENCE_ARCHITECTURES)})")
+    return SEQUENCE_ARCHITECTURES[arch][0].from_dict(raw)

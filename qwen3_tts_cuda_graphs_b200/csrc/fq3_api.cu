@@ -2,6 +2,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <array>
 #include <vector>
@@ -968,8 +969,21 @@ int fq3_predictor_run(fq3_engine* e, int idx, const void* pred_input, const fq3_
 int fq3_sample(fq3_engine* e, const void* logits_f32, int V, const void* history_i64, int n_history,
                const fq3_policy* policy, int eos_id, int suppress_eos, int flags, uint64_t draw_index,
                void* out_token_i64, void* stream) {
-  if (!e || !logits_f32 || !policy || !out_token_i64) return fail(FQ3_E_INVALID, "bad sample arguments");
+  if (!logits_f32 || !policy || !out_token_i64) return fail(FQ3_E_INVALID, "bad sample arguments");
   if (V <= 0 || V > kMaxVocab) return fail(FQ3_E_UNSUPPORTED, "vocab exceeds sampling scratch");
+  // Without an engine (a model that runs on the op-list library samples its logits here too) the repetition-penalty bitmap
+  // lives in a scratch of the calling device, allocated once per device and never freed.
+  uint8_t* seen = e ? e->seen_scratch : nullptr;
+  if (!e) {
+    static uint8_t* dev_scratch[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FQ3_E_INVALID, "device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_scratch[dev]) CK(cudaMalloc(&dev_scratch[dev], (size_t)kMaxVocab * 4));
+    seen = dev_scratch[dev];
+  }
   SampleArgs a{};
   a.V = V; a.do_sample = policy->do_sample; a.top_k = policy->top_k; a.top_p = policy->top_p;
   a.temperature = policy->temperature; a.rep_pen = policy->repetition_penalty; a.seen = nullptr;
@@ -978,8 +992,8 @@ int fq3_sample(fq3_engine* e, const void* logits_f32, int V, const void* history
   a.next_emb = nullptr; a.emb_row_bytes = 0;
   fq3_sample_kernel<<<1, kConsumerThreads, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<const float*>(logits_f32), a, reinterpret_cast<const long long*>(history_i64), n_history,
-      e->seen_scratch, reinterpret_cast<long long*>(out_token_i64));
-  e->launches += 1;
+      seen, reinterpret_cast<long long*>(out_token_i64));
+  if (e) e->launches += 1;
   CK(cudaGetLastError());
   return 0;
 }

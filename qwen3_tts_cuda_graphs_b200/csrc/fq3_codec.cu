@@ -59,8 +59,10 @@ __device__ __forceinline__ void epilogue_pair(const fq3c_op& o, int row, int col
     v0 += b[cm0];
     if (has1) v1 += b[cm1];
   }
-  v0 = bf16r(v0);
-  v1 = bf16r(v1);
+  if (!(o.flags & FQ3C_NOROUND)) {
+    v0 = bf16r(v0);
+    v1 = bf16r(v1);
+  }
   if (o.flags & FQ3C_SWIGLU) {  // interleaved (gate, up) columns -> one output column
     const float y = bf16r(bf16r(silu_f(v0)) * v1);
     reinterpret_cast<bf16*>(o.C)[(size_t)row * o.ldc + (col >> 1)] = __float2bfloat16_rn(y);
@@ -951,6 +953,8 @@ __global__ void fq3c_snake_kernel(const fq3c_op o) {
   }
 }
 
+#include "fq3_seq.cuh"
+
 int fail(const std::string& m) { g_err = m; return -1; }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
@@ -982,11 +986,149 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, u
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// ---- sequence-model ops: launch logic ---------------------------------------------------------------------------------------
+constexpr int SEQ_GEMM_FLAGS = FQ3C_BIAS | FQ3C_GELU | FQ3C_GELU_TANH | FQ3C_SIGMOID | FQ3C_OUT_F32 | FQ3C_F32 | FQ3C_NOROUND | FQ3C_A_F32;
+
+// a_f32 / b_f32: operand types.  exact: keep f32 A values as they are (CUDA cores) instead of rounding them onto the tensor cores.
+int launch_seq_gemm(const SeqGemm& g, bool a_f32, bool b_f32, bool exact, int zcount, int row_tiles, cudaStream_t s) {
+  if (g.flags & ~SEQ_GEMM_FLAGS) return fail("sequence product: unsupported epilogue flag");
+  if (b_f32 && !a_f32) return fail("sequence product: f32 weights need f32 rows");
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0 || zcount <= 0) return 0;
+  const size_t gemv_smem = (size_t)g.M * g.K * sizeof(float);
+  if (!g.seg && g.M <= 8 && gemv_smem <= 96 * 1024) {
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr[dev]) {
+      cudaFuncSetAttribute(fq3s_gemv_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(fq3s_gemv_kernel<float, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(fq3s_gemv_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      attr[dev] = true;
+    }
+    dim3 grid((g.N + 7) / 8, 1, zcount);
+    if (b_f32) fq3s_gemv_kernel<float, float><<<grid, 256, gemv_smem, s>>>(g);
+    else if (a_f32) fq3s_gemv_kernel<float, bf16><<<grid, 256, gemv_smem, s>>>(g);
+    else fq3s_gemv_kernel<bf16, bf16><<<grid, 256, gemv_smem, s>>>(g);
+    return 0;
+  }
+  dim3 grid((g.N + 63) / 64, row_tiles, zcount);
+  if (b_f32) fq3s_gemm_kernel<float, float><<<grid, 256, 0, s>>>(g);
+  else if (a_f32 && exact) fq3s_gemm_kernel<float, bf16><<<grid, 256, 0, s>>>(g);
+  else if (a_f32) fq3s_gemm_mma_kernel<float><<<grid, 128, 0, s>>>(g);
+  else fq3s_gemm_mma_kernel<bf16><<<grid, 128, 0, s>>>(g);
+  return 0;
+}
+
+// returns 1 when the kind is not a sequence-model op
+int seq_run(const fq3c_op& o, cudaStream_t s) {
+  switch (o.kind) {
+    case FQ3C_EMBED:
+      if (!o.A || !o.B || !o.C) return fail("embed: missing operand");
+      if (o.flags & FQ3C_F32) fq3s_embed_kernel<float><<<o.M, 128, 0, s>>>(o);
+      else fq3s_embed_kernel<bf16><<<o.M, 128, 0, s>>>(o);
+      return 0;
+    case FQ3C_TCONV:
+      if (o.taps < 1 || !o.A || !o.B || !o.C || (o.taps > 1 && (!o.p0 || !o.p1))) return fail("tconv: missing operand");
+      fq3s_tconv_kernel<<<dim3((o.N + 255) / 256, o.M + o.taps - 1), 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_GNORM:
+      if (o.i0 < 1 || o.N % o.i0 || !o.scale || ((o.flags & FQ3C_RESID) && !o.res)) return fail("gnorm: groups must divide N; weights required");
+      fq3s_gnorm_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o);
+      return 0;
+    case FQ3C_POLYNORM:
+      if (!o.p0) return fail("polynorm: coefficients required");
+      fq3s_polynorm_kernel<<<o.M, 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_BDGEMM: {
+      if (o.i0 < 1 || o.i1 < 1 || o.i2 < 1 || o.cin < 1) return fail("bdgemm: bad block shape");
+      SeqGemm g{};
+      g.A = o.A; g.B = o.B; g.bias = reinterpret_cast<const float*>(o.bias); g.C = o.C;
+      g.M = o.M; g.N = o.i2; g.K = o.cin; g.lda = o.lda; g.ldb = o.cin; g.ldc = o.ldc; g.flags = o.flags;
+      g.a_mod = o.i1; g.a_zstride = o.cin; g.c_zstride = o.i2; g.b_zstride = (long long)o.i2 * o.cin;
+      return launch_seq_gemm(g, true, (o.flags & FQ3C_F32) != 0, (o.flags & FQ3C_NOROUND) != 0, o.i0, (o.M + 63) / 64, s);
+    }
+    case FQ3C_GGEMM: {
+      if (o.i0 < 1 || !o.p0) return fail("ggemm: segment starts required");
+      SeqGemm g{};
+      g.A = o.A; g.B = o.B; g.bias = nullptr; g.C = o.C;
+      g.M = o.M; g.N = o.N; g.K = o.K; g.lda = o.lda; g.ldb = o.K; g.ldc = o.ldc; g.flags = o.flags & ~FQ3C_BIAS;
+      g.a_mod = 1; g.seg = reinterpret_cast<const int*>(o.p0); g.rows = reinterpret_cast<const int*>(o.p1); g.E = o.i0;
+      g.b_estride = (long long)o.N * o.K;
+      const bool f32 = (o.flags & FQ3C_F32) != 0;
+      return launch_seq_gemm(g, f32 || (o.flags & FQ3C_A_F32), f32, false, 1, (o.M + 63) / 64 + o.i0, s);
+    }
+    case FQ3C_LRU_SCAN: {
+      if (!o.A || !o.B || !o.res || !o.scale || !o.p0 || !o.C || !o.C2) return fail("lru_scan: missing operand");
+      int chunks = 1;
+      if (o.M >= 256 && o.ws) chunks = std::min<int64_t>(std::min(64, o.M / 64), o.ws_bytes / ((int64_t)2 * o.N * 4));
+      chunks = std::max(chunks, 1);
+      const int per = (o.M + chunks - 1) / chunks;
+      dim3 grid((o.N + 127) / 128, chunks);
+      if (chunks > 1) {
+        fq3s_lru_fold_kernel<<<grid, 128, 0, s>>>(o, chunks, per, reinterpret_cast<float*>(o.ws));
+        count_launches(1);
+      }
+      fq3s_lru_scan_kernel<<<grid, 128, 0, s>>>(o, chunks, per, reinterpret_cast<const float*>(o.ws));
+      return 0;
+    }
+    case FQ3C_ROUTER: {
+      if (o.i0 < 1 || o.i0 > o.N || o.i1 < 1 || o.i1 > 64 || o.N % o.i1 || o.i2 < 1 || !o.C || !o.C2) return fail("router: bad configuration");
+      int tpb = (int)std::min<size_t>(128, (48 * 1024) / ((size_t)o.N * 8));
+      if (tpb < 1) return fail("router: too many experts");
+      if (tpb >= 32) tpb &= ~31;
+      fq3s_router_kernel<<<(o.M + tpb - 1) / tpb, tpb, (size_t)o.N * tpb * 8, s>>>(o);
+      return 0;
+    }
+    case FQ3C_MOE_SORT: {
+      if (o.i1 < 1 || !o.A || !o.C || !o.C2 || !o.ws) return fail("moe_sort: missing operand");
+      int nth = (int)std::min<long>(1024, ((48 * 1024) / 4 - o.i1 - 1) / o.i1);
+      if (nth < 1) return fail("moe_sort: too many experts");
+      if (nth >= 32) nth &= ~31;
+      nth = std::min(nth, std::max(32, ((o.M * o.i0 + 31) / 32) * 32));
+      fq3s_moe_sort_kernel<<<1, nth, (size_t)(o.i1 + 1 + (size_t)nth * o.i1) * 4, s>>>(o);
+      return 0;
+    }
+    case FQ3C_MOE_COMBINE:
+      if (!o.A || !o.B || !o.p0 || !o.p1 || !o.ws || !o.C) return fail("moe_combine: missing operand");
+      fq3s_moe_combine_kernel<<<o.M, 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_COMMIT:
+      fq3s_commit_kernel<<<dim3(o.M, 8), 256, 0, s>>>(reinterpret_cast<const long long*>(o.A), reinterpret_cast<int*>(o.C), o.i0);
+      return 0;
+    case FQ3C_LATENT_ATTN: {
+      if (o.i0 < 1 || o.i1 < 1 || !o.A || !o.B || !o.C) return fail("latent_attn: missing operand");
+      const int splits = std::max(1, o.K);
+      if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.i1 + 2) * 4)) return fail("latent_attn: workspace too small for the splits");
+      int HG = std::max(1, std::min(o.i0, o.i2 > 0 ? o.i2 : o.i0));
+      while (HG > 1 && latent_attn_smem(HG, o.i1) > 160 * 1024) --HG;
+      const size_t smem = latent_attn_smem(HG, o.i1);
+      if (smem > 200 * 1024) return fail("latent_attn: latent rank too large for shared memory");
+      static bool attr[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !attr[dev]) {
+        cudaFuncSetAttribute(fq3s_latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(fq3s_latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr[dev] = true;
+      }
+      dim3 grid(o.M, (o.i0 + HG - 1) / HG, splits);
+      if (o.flags & FQ3C_F32) fq3s_latent_attn_kernel<float><<<grid, 256, smem, s>>>(o, HG, splits);
+      else fq3s_latent_attn_kernel<bf16><<<grid, 256, smem, s>>>(o, HG, splits);
+      if (splits > 1) {
+        fq3s_latent_merge_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o, splits);
+        count_launches(1);
+      }
+      return 0;
+    }
+    default: return 1;
+  }
+}
+
 }  // namespace
 
 extern "C" {
 
-int fq3c_abi_version(void) { return 5; }
+int fq3c_abi_version(void) { return 6; }
 const char* fq3c_last_error(void) { return g_err.c_str(); }
 int64_t fq3c_launch_count(void) { return g_launches.load(); }
 
@@ -1014,6 +1156,18 @@ int fq3c_run(const fq3c_op* ops, int n_ops, void* stream) {
     if (o.M <= 0) continue;
     switch (o.kind) {
       case FQ3C_GEMM: {
+        // True 32-bit operands, few rows (decode: weight streaming, one warp per output column) and shapes the tensor-core
+        // kernels do not take (K not a multiple of 8, unaligned rows) go to the sequence-model product.
+        if ((o.flags & (FQ3C_F32 | FQ3C_NOROUND)) && o.taps == 1 &&
+            ((o.flags & FQ3C_F32) || o.M <= 4 || o.K % 8 || o.lda % 8 || (reinterpret_cast<uintptr_t>(o.A) & 15) || (reinterpret_cast<uintptr_t>(o.B) & 15))) {
+          SeqGemm g{};
+          g.A = o.A; g.B = o.B; g.bias = reinterpret_cast<const float*>(o.bias); g.C = o.C;
+          g.M = o.M; g.N = o.N; g.K = o.K; g.lda = o.lda; g.ldb = o.K; g.ldc = o.ldc; g.flags = o.flags;
+          g.a_mod = 1;
+          const bool f32 = (o.flags & FQ3C_F32) != 0;
+          if (launch_seq_gemm(g, f32, f32, true, 1, (o.M + 63) / 64, s) != 0) return -1;
+          break;
+        }
         if (o.K % 8 || o.cin % 8 || o.taps > 8 || o.col_mod <= 0) return fail("gemm: K and cin must be multiples of 8, taps <= 8");
         if (o.m_begin < 0 || o.m_begin >= o.M) return fail("gemm: m_begin outside [0, M)");
         if (o.norm_out && ((o.flags & (FQ3C_SWIGLU | FQ3C_OUT_F32)) || !o.norm_w || o.norm_ld < o.N))
@@ -1155,7 +1309,11 @@ int fq3c_run(const fq3c_op* ops, int n_ops, void* stream) {
         fq3c_advance_kernel<<<1, 1, 0, s>>>(reinterpret_cast<int*>(o.C), o.i0);
         break;
       }
-      default: return fail("unknown op kind");
+      default: {
+        const int rc = seq_run(o, s);
+        if (rc == 1) return fail("unknown op kind");
+        if (rc != 0) return rc;
+      }
     }
     count_launches(1);
     cudaError_t e = cudaGetLastError();

@@ -1,0 +1,657 @@
+// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-23): the pieces a decoder-only
+// language model with a 32-bit residual stream is lowered to.  Included by fq3_codec.cu inside its anonymous namespace.
+//
+// What is 32-bit here whatever the weights' type: norms, softmax scores and weights, router, recurrent state and everything that
+// enters the recurrence, the residual sum.  Products take bf16 (or f32) operands and accumulate in f32.
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over a block of up to 1024 threads; every thread gets the result.  red = 32 floats of shared memory.
+__device__ __forceinline__ float seq_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  return warp_sum(t);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Generic tiled product on the CUDA cores, f32 accumulate: any M, N, K and leading dimensions.  It is the true-32-bit path, the
+// path of shapes the tensor-core kernels do not take, the block-diagonal product (grid.z = block) and the grouped product of a
+// mixture of experts (row tiles resolved against the segment starts on the device).
+// ---------------------------------------------------------------------------------------------------------------------------
+struct SeqGemm {
+  const void* A; const void* B; const float* bias; void* C;
+  int M, N, K, lda, ldb, ldc, flags;
+  int a_mod, a_zstride, c_zstride; long long b_zstride;   // grid.z: A columns (z % a_mod) * a_zstride, B + z * b_zstride, C columns z * c_zstride
+  const int* seg; const int* rows; int E; long long b_estride;
+};
+constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 16;
+
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(256) fq3s_gemm_kernel(const SeqGemm g) {
+  __shared__ float As[SG_BK][SG_BM + 4];
+  __shared__ float Bs[SG_BK][SG_BN + 4];
+  const int tid = threadIdx.x, z = blockIdx.z;
+  int row0, row_end;
+  const TB* Bp = reinterpret_cast<const TB*>(g.B) + (size_t)z * g.b_zstride;
+  if (g.seg) {
+    int t = blockIdx.y, e = 0;
+    row0 = -1; row_end = 0;
+    for (; e < g.E; ++e) {
+      const int s0 = g.seg[e], s1 = g.seg[e + 1];
+      const int nt = (s1 - s0 + SG_BM - 1) / SG_BM;
+      if (t < nt) { row0 = s0 + t * SG_BM; row_end = s1; break; }
+      t -= nt;
+    }
+    if (row0 < 0) return;
+    Bp += (size_t)e * g.b_estride;
+  } else {
+    row0 = blockIdx.y * SG_BM; row_end = g.M;
+  }
+  const int col0 = blockIdx.x * SG_BN;
+  const TA* Ap = reinterpret_cast<const TA*>(g.A) + (size_t)(z % g.a_mod) * g.a_zstride;
+  // loader roles: 4 consecutive k of one row per thread
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int ar = row0 + lr;
+  long long a_row = -1;
+  if (ar < row_end) a_row = g.rows ? g.rows[ar] : ar;
+  const int bn = col0 + lr;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < g.K; k0 += SG_BK) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = k0 + lk + q;
+      As[lk + q][lr] = (a_row >= 0 && k < g.K) ? ldf<TA>(Ap + (size_t)a_row * g.lda + k) : 0.f;
+      Bs[lk + q][lr] = (bn < g.N && k < g.K) ? ldf<TB>(Bp + (size_t)bn * g.ldb + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < SG_BK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  const int ccol = z * g.c_zstride;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= row_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = col0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j];
+      if (g.flags & FQ3C_BIAS) v += g.bias[ccol + n];
+      if (g.flags & FQ3C_GELU) v = gelu_f(v);
+      if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
+      if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+      const size_t ci = (size_t)r * g.ldc + ccol + n;
+      if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+      else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// Same contract on the bf16 tensor cores (mma.sync m16n8k16, f32 accumulate) for bf16 weights: the block-diagonal and grouped
+// products of real-size layers.  64 x 64 x 32 tiles, four warps, each a 32 x 32 quadrant.  A may be f32 (rounded to bf16 as it is
+// staged, which is what a bf16 product does to its operand) and rows may be gathered.
+template <typename TA>
+__global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
+  constexpr int LD = 32 + 8;
+  __shared__ __align__(16) bf16 As[64 * LD];
+  __shared__ __align__(16) bf16 Bs[64 * LD];
+  const int tid = threadIdx.x, z = blockIdx.z, warp = tid >> 5, lane = tid & 31;
+  int row0, row_end;
+  const bf16* Bp = reinterpret_cast<const bf16*>(g.B) + (size_t)z * g.b_zstride;
+  if (g.seg) {
+    int t = blockIdx.y, e = 0;
+    row0 = -1; row_end = 0;
+    for (; e < g.E; ++e) {
+      const int s0 = g.seg[e], s1 = g.seg[e + 1];
+      const int nt = (s1 - s0 + 63) / 64;
+      if (t < nt) { row0 = s0 + t * 64; row_end = s1; break; }
+      t -= nt;
+    }
+    if (row0 < 0) return;
+    Bp += (size_t)e * g.b_estride;
+  } else {
+    row0 = blockIdx.y * 64; row_end = g.M;
+  }
+  const int col0 = blockIdx.x * 64;
+  const TA* Ap = reinterpret_cast<const TA*>(g.A) + (size_t)(z % g.a_mod) * g.a_zstride;
+  // loaders: thread -> (row = tid / 2, 16 consecutive k)
+  const int lr = tid >> 1, lk = (tid & 1) * 16;
+  const int ar = row0 + lr;
+  long long a_row = -1;
+  if (ar < row_end) a_row = g.rows ? g.rows[ar] : ar;
+  const int bn = col0 + lr;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  for (int k0 = 0; k0 < g.K; k0 += 32) {
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      const int k = k0 + lk + q;
+      As[lr * LD + lk + q] = (a_row >= 0 && k < g.K) ? __float2bfloat16_rn(ldf<TA>(Ap + (size_t)a_row * g.lda + k)) : __float2bfloat16_rn(0.f);
+      Bs[lr * LD + lk + q] = (bn < g.N && k < g.K) ? Bp[(size_t)bn * g.ldb + k] : __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; kk += 16) {
+      uint32_t a[2][4], b[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + i * 16 + (lane >> 2), c = kk + (lane & 3) * 2;
+        a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r * LD + c]);
+        a[i][1] = *reinterpret_cast<const uint32_t*>(&As[(r + 8) * LD + c]);
+        a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r * LD + c + 8]);
+        a[i][3] = *reinterpret_cast<const uint32_t*>(&As[(r + 8) * LD + c + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = wn + j * 8 + (lane >> 2), c = kk + (lane & 3) * 2;
+        b[j][0] = *reinterpret_cast<const uint32_t*>(&Bs[n * LD + c]);
+        b[j][1] = *reinterpret_cast<const uint32_t*>(&Bs[n * LD + c + 8]);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma16816(acc[i][j], a[i], b[j][0], b[j][1]);
+    }
+    __syncthreads();
+  }
+  const int ccol = z * g.c_zstride;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = row0 + wm + i * 16 + (lane >> 2) + (q >> 1) * 8;
+        const int n = col0 + wn + j * 8 + (lane & 3) * 2 + (q & 1);
+        if (r >= row_end || n >= g.N) continue;
+        float v = acc[i][j][q];
+        if (g.flags & FQ3C_BIAS) v += g.bias[ccol + n];
+        if (g.flags & FQ3C_GELU) v = gelu_f(v);
+        if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
+        if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+        const size_t ci = (size_t)r * g.ldc + ccol + n;
+        if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+        else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+      }
+}
+
+// One output row with few rows in flight (decode: M <= 8): a warp per output column streams its weight row once, 16 bytes per
+// lane and load, and dots it with every A row (f32 or bf16 in shared memory as f32).  Weight-streaming bound.
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
+  extern __shared__ float xs[];  // [M][K]
+  const int z = blockIdx.z;
+  const TA* Ap = reinterpret_cast<const TA*>(g.A) + (size_t)(z % g.a_mod) * g.a_zstride;
+  const TB* Bp = reinterpret_cast<const TB*>(g.B) + (size_t)z * g.b_zstride;
+  for (int i = threadIdx.x; i < g.M * g.K; i += blockDim.x) {
+    const int m = i / g.K, k = i - m * g.K;
+    xs[i] = ldf<TA>(Ap + (size_t)m * g.lda + k);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= g.N) return;
+  const TB* w = Bp + (size_t)n * g.ldb;
+  float acc[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+  constexpr int VEC = 16 / sizeof(TB);
+  const bool vec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (g.K % VEC == 0);
+  if (vec) {
+    for (int k = lane * VEC; k < g.K; k += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+      float wv[VEC];
+      if (sizeof(TB) == 2) {
+        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { wv[(2 * q) % VEC] = __uint_as_float(u[q] << 16); wv[(2 * q + 1) % VEC] = __uint_as_float(u[q] & 0xffff0000u); }
+      } else {
+        wv[0] = __uint_as_float(raw.x); wv[1] = __uint_as_float(raw.y); wv[2 % VEC] = __uint_as_float(raw.z); wv[3 % VEC] = __uint_as_float(raw.w);
+      }
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (m < g.M) {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) acc[m] = fmaf(wv[q], xs[m * g.K + k + q], acc[m]);
+        }
+    }
+  } else {
+    for (int k = lane; k < g.K; k += 32) {
+      const float wv = ldf<TB>(w + k);
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (m < g.M) acc[m] = fmaf(wv, xs[m * g.K + k], acc[m]);
+    }
+  }
+  const int ccol = z * g.c_zstride;
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    if (m >= g.M) break;
+    float v = warp_sum(acc[m]);
+    if (lane == 0) {
+      if (g.flags & FQ3C_BIAS) v += g.bias[ccol + n];
+      if (g.flags & FQ3C_GELU) v = gelu_f(v);
+      if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
+      if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+      const size_t ci = (size_t)m * g.ldc + ccol + n;
+      if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+      else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename TB>
+__global__ void fq3s_embed_kernel(const fq3c_op o) {
+  const int m = blockIdx.x;
+  const int id = reinterpret_cast<const int*>(o.A)[m];
+  const TB* row = reinterpret_cast<const TB*>(o.B) + (size_t)id * o.N;
+  float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc;
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) c[i] = ldf<TB>(row + i);
+}
+
+// grid (ceil(N / 256), M + taps - 1): rows >= M write the next history
+__global__ void __launch_bounds__(256) fq3s_tconv_kernel(const fq3c_op o) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= o.N) return;
+  const int m = blockIdx.y, h = o.taps - 1;
+  const float* x = reinterpret_cast<const float*>(o.A);
+  const float* hist = reinterpret_cast<const float*>(o.p0);
+  if (m >= o.M) {
+    const int s = m - o.M, pos = o.M - h + s;
+    reinterpret_cast<float*>(const_cast<void*>(o.p1))[(size_t)s * o.N + c] = pos >= 0 ? x[(size_t)pos * o.lda + c] : hist[(size_t)(h + pos) * o.N + c];
+    return;
+  }
+  const float* w = reinterpret_cast<const float*>(o.B) + (size_t)c * o.taps;
+  float a = (o.flags & FQ3C_BIAS) ? reinterpret_cast<const float*>(o.bias)[c] : 0.f;
+  for (int j = 0; j < o.taps; ++j) {
+    const int pos = m - h + j;
+    const float v = pos >= 0 ? x[(size_t)pos * o.lda + c] : hist[(size_t)(h + pos) * o.N + c];
+    a = fmaf(w[j], v, a);
+  }
+  if (o.flags & FQ3C_RESID) a += x[(size_t)m * o.lda + c];
+  if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + c] = a;
+  else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(a);
+}
+
+// grid (M, groups); one block per (row, group)
+__global__ void __launch_bounds__(128) fq3s_gnorm_kernel(const fq3c_op o) {
+  __shared__ float red[32];
+  const int m = blockIdx.x, gsz = o.N / o.i0, c0 = blockIdx.y * gsz;
+  const float* x = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < gsz; i += blockDim.x) { const float v = x[i]; ss = fmaf(v, v, ss); }
+  ss = seq_block_sum(ss, red);
+  const float rs = 1.f / sqrtf(ss / (float)gsz + o.f0);
+  const float* w = reinterpret_cast<const float*>(o.scale) + c0;
+  const size_t orow = (size_t)m + (o.p0 ? (size_t)*reinterpret_cast<const int*>(o.p0) : 0);
+  for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
+    float v = x[i] * rs * w[i];
+    if (o.flags & FQ3C_RESID) v += reinterpret_cast<const float*>(o.res)[(size_t)m * o.ldr + c0 + i];
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[orow * o.ldc + c0 + i] = v;
+    else reinterpret_cast<bf16*>(o.C)[orow * o.ldc + c0 + i] = __float2bfloat16_rn(v);
+    if (o.C2) reinterpret_cast<bf16*>(o.C2)[orow * o.ldc + c0 + i] = __float2bfloat16_rn(v);
+  }
+}
+
+__global__ void __launch_bounds__(256) fq3s_polynorm_kernel(const fq3c_op o) {
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const float* x = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
+  const float* p = reinterpret_cast<const float*>(o.p0);
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    const float z = x[i], z2 = z * z, z3 = z2 * z;
+    s1 = fmaf(z, z, s1); s2 = fmaf(z2, z2, s2); s3 = fmaf(z3, z3, s3);
+  }
+  s1 = seq_block_sum(s1, red); s2 = seq_block_sum(s2, red); s3 = seq_block_sum(s3, red);
+  const float inv = 1.f / (float)o.N;
+  const float r1 = p[0] / sqrtf(s1 * inv + o.f0), r2 = p[1] / sqrtf(s2 * inv + o.f0), r3 = p[2] / sqrtf(s3 * inv + o.f0), e = p[3];
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    const float z = x[i], z2 = z * z, z3 = z2 * z;
+    const float v = r1 * z + r2 * z2 + r3 * z3 + e;
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + i] = v;
+    else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Gated diagonal linear recurrence.  The recurrence S_t = a_t S_(t-1) + b_t is associative in (a, b), so a long run of rows is
+// cut into `chunks` pieces: pass 0 folds every piece from a zero state into (prod a, local S), pass 1 walks the pieces' carries in
+// order and writes the outputs.  grid (ceil(N / 128), chunks).  A single piece (decode, short runs) does everything in pass 1.
+// ---------------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void lru_coeffs(const fq3c_op& o, int t, int c, float sp, float& a, float& b) {
+  const float* g = reinterpret_cast<const float*>(o.A) + (size_t)t * o.lda;
+  const float r = g[c], ig = g[o.N + c];
+  const float u = reinterpret_cast<const float*>(o.B)[(size_t)t * o.cin + c];
+  const float la = -o.f0 * r * sp;
+  a = expf(la);
+  b = sqrtf(fmaxf(-expm1f(2.f * la), 0.f)) * ig * u;
+}
+__global__ void __launch_bounds__(128) fq3s_lru_fold_kernel(const fq3c_op o, const int chunks, const int per, float* carry) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, q = blockIdx.y;
+  if (c >= o.N) return;
+  const float sp = softplus_f(reinterpret_cast<const float*>(o.scale)[c]);
+  const int t0 = q * per, t1 = min(o.M, t0 + per);
+  float pa = 1.f, s = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    float a, b;
+    lru_coeffs(o, t, c, sp, a, b);
+    s = fmaf(a, s, b);
+    pa *= a;
+  }
+  carry[((size_t)q * 2) * o.N + c] = pa;
+  carry[((size_t)q * 2 + 1) * o.N + c] = s;
+}
+__global__ void __launch_bounds__(128) fq3s_lru_scan_kernel(const fq3c_op o, const int chunks, const int per, const float* carry) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, q = blockIdx.y;
+  if (c >= o.N) return;
+  const float sp = softplus_f(reinterpret_cast<const float*>(o.scale)[c]);
+  float* state = reinterpret_cast<float*>(const_cast<void*>(o.p0));
+  float s = state[c];
+  for (int j = 0; j < q; ++j) s = fmaf(carry[((size_t)j * 2) * o.N + c], s, carry[((size_t)j * 2 + 1) * o.N + c]);
+  const int t0 = q * per, t1 = min(o.M, t0 + per);
+  const float* y = reinterpret_cast<const float*>(o.res);
+  for (int t = t0; t < t1; ++t) {
+    float a, b;
+    lru_coeffs(o, t, c, sp, a, b);
+    s = fmaf(a, s, b);
+    const float v = s * gelu_tanh_f(y[(size_t)t * o.ldr + c]);
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)t * o.ldc + c] = v;
+    else reinterpret_cast<bf16*>(o.C)[(size_t)t * o.ldc + c] = __float2bfloat16_rn(v);
+  }
+  // the last piece owns the state; every piece read it before (stream order: the fold pass never touches it, and within this
+  // launch only the last piece writes) — so the write goes to the staging copy C2 and FQ3C_COMMIT installs it
+  if (q == chunks - 1) reinterpret_cast<float*>(o.C2)[c] = s;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Router: one thread per token, its scores in shared memory [n][threads].
+// ---------------------------------------------------------------------------------------------------------------------------
+__global__ void fq3s_router_kernel(const fq3c_op o) {
+  extern __shared__ float rsm[];
+  const int tpb = blockDim.x, n = o.N, tx = threadIdx.x;
+  const int m = blockIdx.x * tpb + tx;
+  if (m >= o.M) return;
+  float* s = rsm + tx;                       // s[i * tpb]
+  float* ch = rsm + (size_t)n * tpb + tx;    // choice scores
+  const float* z = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
+  const float* corr = reinterpret_cast<const float*>(o.bias);
+  float mx = -INFINITY;
+  for (int i = 0; i < n; ++i) mx = fmaxf(mx, z[i]);
+  float sum = 0.f;
+  for (int i = 0; i < n; ++i) { const float e = expf(z[i] - mx); s[i * tpb] = e; sum += e; }
+  const float inv = 1.f / sum;
+  for (int i = 0; i < n; ++i) { const float v = s[i * tpb] * inv; s[i * tpb] = v; ch[i * tpb] = v + (corr ? corr[i] : 0.f); }
+  const int G = o.i1, keep = o.i2, gsz = n / max(G, 1);
+  if (G > 1 && keep < G) {
+    unsigned long long kept = 0ull;
+    for (int k = 0; k < keep; ++k) {
+      int best = -1; float bv = 0.f;
+      for (int gq = 0; gq < G; ++gq) {
+        if ((kept >> gq) & 1ull) continue;
+        float gm = -INFINITY;
+        for (int i = 0; i < gsz; ++i) gm = fmaxf(gm, ch[(gq * gsz + i) * tpb]);
+        if (best < 0 || gm > bv) { best = gq; bv = gm; }
+      }
+      kept |= 1ull << best;
+    }
+    for (int gq = 0; gq < G; ++gq)
+      if (!((kept >> gq) & 1ull))
+        for (int i = 0; i < gsz; ++i) ch[(gq * gsz + i) * tpb] = -INFINITY;
+  }
+  int* ids = reinterpret_cast<int*>(o.C) + (size_t)m * o.i0;
+  float* wt = reinterpret_cast<float*>(o.C2) + (size_t)m * o.i0;
+  float wsum = 0.f;
+  for (int k = 0; k < o.i0; ++k) {
+    int best = -1; float bv = 0.f;
+    for (int i = 0; i < n; ++i) {
+      const float v = ch[i * tpb];
+      if (v == -INFINITY) continue;
+      if (best < 0 || v > bv) { best = i; bv = v; }
+    }
+    if (best < 0) best = 0;   // fewer eligible experts than asked for: cannot happen with a consistent configuration
+    ch[best * tpb] = -INFINITY;
+    ids[k] = best;
+    const float sv = s[best * tpb];
+    wt[k] = sv;
+    wsum += sv;
+  }
+  const float sc = o.f0 / (wsum + 1e-20f);
+  for (int k = 0; k < o.i0; ++k) wt[k] *= sc;
+}
+
+// One block.  Counting sort of the (token, choice) pairs by expert, token order kept inside an expert.
+__global__ void __launch_bounds__(1024) fq3s_moe_sort_kernel(const fq3c_op o) {
+  extern __shared__ int ssm[];   // [E + 1] starts, then [nchunk][E] counts
+  const int E = o.i1, n = o.M * o.i0, nth = blockDim.x;
+  const int* ids = reinterpret_cast<const int*>(o.A);
+  int* seg = reinterpret_cast<int*>(o.C);
+  int* rows = reinterpret_cast<int*>(o.C2);
+  int* pos = reinterpret_cast<int*>(o.ws);
+  int* start = ssm;
+  int* cnt = ssm + E + 1;        // cnt[t * E + e]: entries of expert e in thread t's contiguous share
+  const int per = (n + nth - 1) / nth;
+  const int i0 = threadIdx.x * per, i1 = min(n, i0 + per);
+  for (int e = 0; e < E; ++e) cnt[threadIdx.x * E + e] = 0;
+  for (int i = i0; i < i1; ++i) { const int e = ids[i]; if (e < E) cnt[threadIdx.x * E + e] += 1; }
+  __syncthreads();
+  // per expert: exclusive scan over the threads' shares (thread e walks column e)
+  for (int e = threadIdx.x; e < E; e += nth) {
+    int run = 0;
+    for (int t = 0; t < nth; ++t) { const int v = cnt[t * E + e]; cnt[t * E + e] = run; run += v; }
+    start[e + 1] = run;   // total, turned into starts below
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    start[0] = 0;
+    for (int e = 0; e < E; ++e) { const int v = start[e + 1]; start[e] = run; run += v; }
+    start[E] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += nth) seg[e] = start[e];
+  for (int i = i0; i < i1; ++i) {
+    const int e = ids[i];
+    if (e < E) {
+      const int p = start[e] + cnt[threadIdx.x * E + e]++;
+      rows[p] = i / o.i0;
+      pos[i] = p;
+    } else {
+      pos[i] = -1;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) fq3s_moe_combine_kernel(const fq3c_op o) {
+  const int m = blockIdx.x, top = o.i0;
+  const int* ids = reinterpret_cast<const int*>(o.p0) + (size_t)m * top;
+  const float* w = reinterpret_cast<const float*>(o.p1) + (size_t)m * top;
+  const int* pos = reinterpret_cast<const int*>(o.ws) + (size_t)m * top;
+  const float* Y = reinterpret_cast<const float*>(o.A);
+  const float* x = reinterpret_cast<const float*>(o.B) + (size_t)m * o.ldr;
+  const float* sh = o.res ? reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr : nullptr;
+  float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc;
+  for (int i = threadIdx.x; i < o.N; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const float v = ids[j] >= o.i1 ? x[i] : Y[(size_t)pos[j] * o.lda + i];
+      acc = fmaf(w[j], v, acc);
+    }
+    if (sh) acc += sh[i];
+    c[i] = acc;
+  }
+}
+
+// grid (copies, 8)
+__global__ void __launch_bounds__(256) fq3s_commit_kernel(const long long* desc, int* counter, int by) {
+  const long long* d = desc + (size_t)blockIdx.x * 3;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(d[0]);
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(d[1]);
+  const long long n = d[2] >> 2;
+  for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.y * blockDim.x) dst[i] = src[i];
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && counter) *counter += by;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Latent attention, absorbed form: all heads of a group share the latent rows, so a block stages a tile of TJ rows once and every
+// head scores it.  grid (M, head groups, splits), 256 threads.  Shared memory (f32): q [HG][R], tile [TJ][R + 1], p [HG][TJ],
+// out [HG][R], running max / sum / rescale [3][HG].  Online softmax over the tiles; a single split finishes in place (sink
+// included), several leave (max, sum, out) per split in ws and fq3s_latent_merge_kernel finishes.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int LA_TJ = 32;
+__host__ __device__ inline size_t latent_attn_smem(int HG, int R) {
+  return sizeof(float) * ((size_t)HG * R * 2 + (size_t)LA_TJ * (R + 1) + (size_t)HG * LA_TJ + 3 * (size_t)HG);
+}
+template <typename TC>
+__global__ void __launch_bounds__(256) fq3s_latent_attn_kernel(const fq3c_op o, const int HG, const int splits) {
+  extern __shared__ float lsm[];
+  const int R = o.i1, H = o.i0, m = blockIdx.x, h0 = blockIdx.y * HG, z = blockIdx.z;
+  const int hg = min(HG, H - h0);
+  float* qs = lsm;
+  float* os = qs + (size_t)HG * R;
+  float* tile = os + (size_t)HG * R;
+  float* sc = tile + (size_t)LA_TJ * (R + 1);
+  float* mx = sc + (size_t)HG * LA_TJ;
+  float* ls = mx + HG;
+  float* al = ls + HG;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
+  const int nkeys = P + m + 1;
+  int per = (nkeys + splits - 1) / splits;
+  per = (per + LA_TJ - 1) / LA_TJ * LA_TJ;
+  const int j0 = z * per, j1 = min(nkeys, j0 + per);
+  const float* q = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + (size_t)h0 * R;
+  for (int i = tid; i < hg * R; i += blockDim.x) { qs[i] = q[i] * o.f0; os[i] = 0.f; }
+  for (int i = tid; i < hg; i += blockDim.x) { mx[i] = -INFINITY; ls[i] = 0.f; }
+  const TC* cache = reinterpret_cast<const TC*>(o.B);
+  __syncthreads();
+  for (int jt = j0; jt < j1; jt += LA_TJ) {
+    for (int i = tid; i < LA_TJ * R; i += blockDim.x) {
+      const int j = i / R, r = i - j * R;
+      tile[j * (R + 1) + r] = (jt + j < j1) ? ldf<TC>(cache + (size_t)(jt + j) * o.ldr + r) : 0.f;
+    }
+    __syncthreads();
+    for (int i = tid; i < hg * LA_TJ; i += blockDim.x) {
+      const int h = i / LA_TJ, j = i - h * LA_TJ;
+      const float* qq = qs + (size_t)h * R;
+      const float* tt = tile + (size_t)j * (R + 1);
+      float d0 = 0.f, d1 = 0.f;
+      int r = 0;
+      for (; r + 1 < R; r += 2) { d0 = fmaf(qq[r], tt[r], d0); d1 = fmaf(qq[r + 1], tt[r + 1], d1); }
+      if (r < R) d0 = fmaf(qq[r], tt[r], d0);
+      sc[i] = (jt + j < j1) ? d0 + d1 : -INFINITY;
+    }
+    __syncthreads();
+    for (int h = warp; h < hg; h += (blockDim.x >> 5)) {   // LA_TJ == 32: one lane per key of the tile
+      const float s = sc[h * LA_TJ + lane];
+      const float tm = warp_max(s);
+      const float mo = mx[h], mn = fmaxf(mo, tm);
+      const float p = s == -INFINITY ? 0.f : expf(s - mn);
+      const float ps = warp_sum(p);
+      sc[h * LA_TJ + lane] = p;
+      if (lane == 0) {
+        const float a = mo == -INFINITY ? 0.f : expf(mo - mn);
+        al[h] = a; ls[h] = ls[h] * a + ps; mx[h] = mn;
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < hg * R; i += blockDim.x) {
+      const int h = i / R, r = i - h * R;
+      float acc = os[i] * al[h];
+      const float* pp = sc + h * LA_TJ;
+#pragma unroll 8
+      for (int j = 0; j < LA_TJ; ++j) acc = fmaf(pp[j], tile[j * (R + 1) + r], acc);
+      os[i] = acc;
+    }
+    __syncthreads();
+  }
+  if (splits == 1) {
+    const float* sink = reinterpret_cast<const float*>(o.scale);
+    float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h0 * R;
+    for (int i = tid; i < hg * R; i += blockDim.x) {
+      const int h = i / R;
+      float den = ls[h], f = 1.f;
+      if (sink) {
+        const float sk = sink[h0 + h], mm = fmaxf(mx[h], sk);
+        f = expf(mx[h] - mm);
+        den = ls[h] * f + expf(sk - mm);
+      }
+      c[i] = os[i] * f / den;
+    }
+  } else {
+    float* ws = reinterpret_cast<float*>(o.ws);
+    // partial state of (m, head, split): [max, sum] then R outputs
+    for (int i = tid; i < hg * R; i += blockDim.x) {
+      const int h = i / R, r = i - h * R;
+      float* dst = ws + (((size_t)m * H + h0 + h) * splits + z) * (R + 2);
+      dst[2 + r] = os[i];
+      if (r == 0) { dst[0] = mx[h]; dst[1] = ls[h]; }
+    }
+  }
+}
+// grid (M, H)
+__global__ void __launch_bounds__(128) fq3s_latent_merge_kernel(const fq3c_op o, const int splits) {
+  const int R = o.i1, H = o.i0, m = blockIdx.x, h = blockIdx.y;
+  const float* base = reinterpret_cast<const float*>(o.ws) + ((size_t)m * H + h) * splits * (R + 2);
+  const float* sink = reinterpret_cast<const float*>(o.scale);
+  float mm = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[(size_t)s * (R + 2)]);
+  float den = sink ? expf(sink[h] - mm) : 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = base[(size_t)s * (R + 2)];
+    if (ms != -INFINITY) den += base[(size_t)s * (R + 2) + 1] * expf(ms - mm);
+  }
+  float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h * R;
+  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = base[(size_t)s * (R + 2)];
+      if (ms != -INFINITY) acc = fmaf(base[(size_t)s * (R + 2) + 2 + r], expf(ms - mm), acc);
+    }
+    c[r] = acc / den;
+  }
+}

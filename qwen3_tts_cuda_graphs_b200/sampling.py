@@ -49,13 +49,16 @@ def sample_logits(
     do_sample: bool,
     suppress_mask: Optional[torch.Tensor] = None,
     suppress_tokens: Optional[Iterable[int]] = None,
-    engine: Optional[Engine] = None,
+    engine=None,
     seed: int = 0,
     draw_index: Optional[int] = None,
 ) -> torch.Tensor:
-    """sampling.py:32-66 on the GPU.  logits [1, V] (or [V]) -> int64 [1]."""
+    """sampling.py:32-66 on the GPU.  logits [1, V] (or [V]) -> int64 [1].
+
+    `engine=False` samples without a TTS engine: the same kernel through the library's engine-less entry (the sequence models'
+    generation path)."""
     global _draw_counter
-    e = _engine(engine)
+    e = None if engine is False else _engine(engine)
     x = logits.reshape(-1)
     if suppress_mask is not None or suppress_tokens:
         x = x.clone()
@@ -68,4 +71,25 @@ def sample_logits(
         _draw_counter += 1
     pol = SamplingPolicy(do_sample=do_sample, top_k=top_k, top_p=top_p, temperature=temperature,
                          repetition_penalty=1.0, min_new_tokens=0, suppress_tail=0, seed=seed)
+    if e is None:
+        return sample_row_standalone(x, pol, draw_index)
     return e.sample(x, None, pol, eos_id=-1, suppress_eos=False, draw_index=draw_index)
+
+
+def sample_row_standalone(logits: torch.Tensor, pol: SamplingPolicy, draw_index: int = 0) -> torch.Tensor:
+    """`fq3_sample` without an engine handle: one row of logits on a CUDA device -> int64 [1] on that device."""
+    import ctypes as C
+
+    from . import _lib
+
+    if not logits.is_cuda:
+        raise RuntimeError("fq3 sampling runs on CUDA tensors only (no CPU fallback)")
+    lib = _lib.load()
+    flags = 1 if logits.dtype == torch.bfloat16 else 0
+    lg = logits.reshape(-1).to(torch.float32).contiguous()
+    out = torch.empty(1, dtype=torch.int64, device=logits.device)
+    c = pol.c()
+    with torch.cuda.device(logits.device):
+        _lib.check(lib.fq3_sample(None, lg.data_ptr(), lg.numel(), None, 0, C.byref(c), -1, 0, flags, int(draw_index), out.data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream))
+    return out

@@ -1,0 +1,218 @@
+"""Mechanisms of the sequence models as op-list fragments (include/fq3_codec.h, kinds 12-23).
+
+A `StepBuilder` lowers ONE step (M new tokens of the request in one slot) to a flat list of `fq3c_op` records over buffers
+it allocates; the list is handed to `fq3c_run` / replayed as a CUDA graph like the codec's plans.  Each mechanism is a method
+with its constants as arguments, so another design composes them differently:
+
+  embed, time_conv (causal per-channel convolution with carried inputs), group_norm (RMS norm in groups, optional residual
+  add), linear (tcgen05 GEMM, or the CUDA-core / GEMV product for true 32-bit, decode rows and odd shapes), latent_attention
+  (low-rank shared latent cache, absorbed projections, sink softmax), rglru (gated diagonal linear recurrence block),
+  polynorm_ff, moe_ff (softmax router with correction, neighbour groups, identity experts, shared expert).
+
+Precision: `f32=True` runs every product in true 32-bit.  Otherwise weights and product operands are bf16 with f32
+accumulation; the residual stream, norms, softmax, router, recurrence and everything entering it are f32 in both modes.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .codec import (F_A_F32, F_BIAS, F_F32, F_GELU, F_NOROUND, F_OUT_F32, F_RESID, F_SIGMOID, K_BDGEMM, K_COMMIT, K_EMBED, K_GEMM,
+                    K_GGEMM, K_GNORM, K_LATENT_ATTN, K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_POLYNORM, K_ROUTER, K_TCONV, Op, _Plan)
+from .config import LatentAttentionConfig, MoEFFConfig, RglruConfig
+from .seq_state import SlotState
+
+
+def _ptr(t: Optional[torch.Tensor], col: int = 0) -> Optional[int]:
+    return None if t is None else t.data_ptr() + col * t.element_size()
+
+
+class StepBuilder:
+    def __init__(self, device, M: int, slot: SlotState, f32: bool):
+        self.device, self.M, self.slot, self.f32 = device, int(M), slot, bool(f32)
+        self.adt = torch.float32 if f32 else torch.bfloat16     # dtype of product operands
+        self.plan = _Plan()
+        self._pool: Dict[tuple, torch.Tensor] = {}
+
+    # ---- buffers --------------------------------------------------------------------------------
+    def buf(self, name: str, rows: int, cols: int, dtype=torch.float32) -> torch.Tensor:
+        """A scratch buffer, shared by every layer that asks for the same (name, shape, dtype): ops run in order."""
+        key = (name, rows, cols, dtype)
+        t = self._pool.get(key)
+        if t is None:
+            t = self._pool[key] = torch.zeros(max(rows, 1), cols, dtype=dtype, device=self.device)
+            self.plan.keep.append(t)
+        return t
+
+    def _op(self, kind: int, **kw) -> Op:
+        o = Op()
+        o.kind = kind
+        o.col_mod = 1
+        for k, v in kw.items():
+            if isinstance(v, torch.Tensor):
+                self.plan.keep.append(v)
+                v = v.data_ptr()
+            setattr(o, k, v)
+        self.plan.ops.append(o)
+        return o
+
+    def _oflag(self, out: torch.Tensor) -> int:
+        return F_OUT_F32 if out.dtype == torch.float32 else 0
+
+    # ---- mechanisms -----------------------------------------------------------------------------
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None):
+        """out f32 [rows, N] = table[ids]; also a row gather from an f32 matrix (F_F32)."""
+        self._op(K_EMBED, M=rows or self.M, N=table.shape[1], A=ids, B=table, C=out, ldc=out.shape[1],
+                 flags=F_F32 if table.dtype == torch.float32 else 0)
+        return out
+
+    def time_conv(self, x: torch.Tensor, w: torch.Tensor, state: str, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  add_input: bool = False, col: int = 0, channels: Optional[int] = None):
+        """out = (x if add_input) + bias + causal conv over time of x's columns [col, col + channels); w f32 [channels, taps]."""
+        taps = w.shape[1]
+        n = channels or w.shape[0]
+        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_RESID if add_input else 0)
+        kw = dict(M=self.M, N=n, taps=taps, A=_ptr(x, col), lda=x.shape[1], B=w, C=out, ldc=out.shape[1], flags=flags)
+        if bias is not None:
+            kw["bias"] = bias
+        if taps > 1:
+            kw["p0"], kw["p1"] = self.slot.cur[state], self.slot.next[state]
+        self.plan.keep += [x]
+        self._op(K_TCONV, **kw)
+        return out
+
+    def group_norm(self, x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, out: torch.Tensor, n: Optional[int] = None,
+                   col: int = 0, residual: Optional[torch.Tensor] = None, out_bf16: Optional[torch.Tensor] = None,
+                   append_at_position: bool = False):
+        n = n or w.shape[0]
+        kw = dict(M=self.M, N=n, i0=groups, f0=eps, A=_ptr(x, col), lda=x.shape[1], scale=w, C=out, ldc=out.shape[1],
+                  flags=self._oflag(out) | (F_RESID if residual is not None else 0))
+        if residual is not None:
+            kw["res"], kw["ldr"] = residual, residual.shape[1]
+        if out_bf16 is not None:
+            kw["C2"] = out_bf16
+        if append_at_position:
+            kw["p0"] = self.slot.pos
+        self.plan.keep += [x]
+        self._op(K_GNORM, **kw)
+        return out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+               rows: Optional[int] = None, force_f32: bool = False):
+        """out = act(x W^T + bias).  x and W share a type (bf16, or f32 for true 32-bit: `force_f32` for a router)."""
+        M = rows or self.M
+        N, K = w.shape
+        f32 = w.dtype == torch.float32
+        assert x.dtype == w.dtype, (x.dtype, w.dtype)
+        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_GELU if gelu else 0) | (F_F32 if f32 else 0)
+        if out.dtype == torch.float32:
+            flags |= F_NOROUND
+        kw = dict(M=M, N=N, K=K, taps=1, cin=K, a_rows=x.shape[0], lda=x.shape[1], ldc=out.shape[1], col_mod=N, A=x, B=w, C=out, flags=flags)
+        if bias is not None:
+            kw["bias"] = bias
+        o = self._op(K_GEMM, **kw)
+        o.tap_off[0] = 0
+        return out
+
+    def block_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, in_blocks: Optional[int] = None,
+                     bias: Optional[torch.Tensor] = None, sigmoid: bool = False, exact: bool = False, col: int = 0):
+        """Block-diagonal product: w [blocks, n_out, n_in]; block b reads x columns col + (b % in_blocks) * n_in ..."""
+        blocks, n_out, n_in = w.shape
+        flags = (self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_SIGMOID if sigmoid else 0) | (F_NOROUND if exact else 0)
+                 | (F_F32 if w.dtype == torch.float32 else 0))
+        kw = dict(M=self.M, N=blocks * n_out, i0=blocks, i1=in_blocks or blocks, i2=n_out, cin=n_in, A=_ptr(x, col), lda=x.shape[1],
+                  B=w, C=out, ldc=out.shape[1], flags=flags)
+        if bias is not None:
+            kw["bias"] = bias
+        self.plan.keep += [x]
+        self._op(K_BDGEMM, **kw)
+        return out
+
+    def latent_attention(self, h: torch.Tensor, c: LatentAttentionConfig, w: dict, cache: str, eps: float, out: torch.Tensor):
+        """h [M, width] (product-operand dtype) -> out f32 [M, width].  w: wqd [H*dim + rank, width], dkv_norm f32 [rank],
+        uk_t [H, rank, dim] (the key up-projection per head, transposed: queries are carried into latent space), uv [H, vdim, rank],
+        sink f32 [H] or None, o [width, H*vdim]."""
+        M, H, R = self.M, c.heads, c.kv_rank
+        qd = self.linear(h, w["wqd"], self.buf("la.qd", M, H * c.dim + R))
+        ctab = self.slot.cur[cache]
+        self.group_norm(qd, w["dkv_norm"], 1, eps, ctab, n=R, col=H * c.dim, append_at_position=True)
+        qa = self.block_linear(qd, w["uk_t"], self.buf("la.qa", M, H * R))
+        splits = 1 if M >= 64 else (4 if M > 8 else 16)
+        oa = self.buf("la.oa", M, H * R)
+        kw = dict(M=M, N=H * R, K=splits, i0=H, i1=R, i2=H, f0=c.scale, A=qa, lda=qa.shape[1], B=ctab, ldr=ctab.shape[1], p0=self.slot.pos,
+                  C=oa, ldc=oa.shape[1], flags=F_F32 if ctab.dtype == torch.float32 else 0)
+        if w.get("sink") is not None:
+            kw["scale"] = w["sink"]
+        if splits > 1:
+            ws = self.buf("la.ws", 1, M * H * splits * (R + 2))
+            kw["ws"], kw["ws_bytes"] = ws, ws.numel() * 4
+        self._op(K_LATENT_ATTN, **kw)
+        ov = self.block_linear(oa, w["uv"], self.buf("la.ov", M, H * c.vdim, self.adt))
+        return self.linear(ov, w["o"], out)
+
+    def rglru(self, h: torch.Tensor, c: RglruConfig, w: dict, state: str, out: torch.Tensor):
+        """h [M, width] -> out f32 [M, width].  w: wyx [2W, width] (gelu branch | recurrent branch), byx f32 [2W] or None,
+        conv f32 [W, taps], conv_b f32 [W] or None, gates [2 * blocks, bs, bs] (recurrence gate blocks, then input gate blocks),
+        gates_b f32 [2W] or None, lam f32 [W], o [width, W]."""
+        M, W = self.M, c.width
+        yx = self.linear(h, w["wyx"], self.buf("lru.yx", M, 2 * W), bias=w.get("byx"))
+        u = self.time_conv(yx, w["conv"], state + ".conv", self.buf("lru.u", M, W), bias=w.get("conv_b"), col=W, channels=W)
+        g = self.block_linear(u, w["gates"], self.buf("lru.g", M, 2 * W), in_blocks=c.blocks, bias=w.get("gates_b"), sigmoid=True, exact=True)
+        sy = self.buf("lru.sy", M, W, self.adt)
+        ws = self.buf("lru.ws", 1, 2 * 64 * W)
+        self._op(K_LRU_SCAN, M=M, N=W, f0=c.decay, A=g, lda=g.shape[1], B=u, cin=u.shape[1], res=yx, ldr=yx.shape[1], scale=w["lam"],
+                 p0=self.slot.cur[state + ".s"], C2=self.slot.next[state + ".s"], C=sy, ldc=sy.shape[1], flags=self._oflag(sy),
+                 ws=ws, ws_bytes=ws.numel() * 4)
+        return self.linear(sy, w["o"], out)
+
+    def polynorm_ff(self, x: torch.Tensor, w: dict, eps: float, out: torch.Tensor):
+        """out f32 = W_down polynorm(W_up x); w: up [ff, width], down [width, ff], act f32 [4]."""
+        ff = w["up"].shape[0]
+        z = self.linear(x, w["up"], self.buf("ff.z", self.M, ff))
+        za = self.buf("ff.za", self.M, ff, self.adt)
+        self._op(K_POLYNORM, M=self.M, N=ff, f0=eps, A=z, lda=ff, p0=w["act"], C=za, ldc=ff, flags=self._oflag(za))
+        return self.linear(za, w["down"], out)
+
+    def moe_ff(self, x32: torch.Tensor, xop: torch.Tensor, c: MoEFFConfig, w: dict, out: torch.Tensor):
+        """x32: the f32 rows (router input, identity experts); xop: the same rows as product operands.  w: router f32 [n, width],
+        correction f32 [n] or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None."""
+        M, n, top, E = self.M, c.routed, c.top, c.experts
+        width = x32.shape[1]
+        z = self.linear(x32, w["router"], self.buf("moe.z", M, n))
+        ids = self.buf("moe.ids", M, top, torch.int32)
+        wt = self.buf("moe.w", M, top)
+        kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt)
+        if w.get("correction") is not None:
+            kw["bias"] = w["correction"]
+        self._op(K_ROUTER, **kw)
+        seg = self.buf("moe.seg", 1, E + 1, torch.int32)
+        rows = self.buf("moe.rows", 1, M * top, torch.int32)
+        pos = self.buf("moe.pos", M, top, torch.int32)
+        self._op(K_MOE_SORT, M=M, i0=top, i1=E, A=ids, C=seg, C2=rows, ws=pos)
+        ff = c.expert_ff
+        f32 = xop.dtype == torch.float32
+        act = self.buf("moe.act", M * top, ff, self.adt)
+        self._op(K_GGEMM, M=M * top, N=ff, K=width, i0=E, A=xop, lda=width, B=w["up"], p0=seg, p1=rows, C=act, ldc=ff,
+                 flags=F_GELU | self._oflag(act) | (F_F32 if f32 else 0))
+        y = self.buf("moe.y", M * top, width)
+        self._op(K_GGEMM, M=M * top, N=width, K=ff, i0=E, A=act, lda=ff, B=w["down"], p0=seg, C=y, ldc=width,
+                 flags=F_OUT_F32 | (F_F32 if f32 else 0))
+        sh = None
+        if w.get("shared_up") is not None:
+            sa = self.linear(xop, w["shared_up"], self.buf("moe.sa", M, w["shared_up"].shape[0], self.adt), gelu=True)
+            sh = self.linear(sa, w["shared_down"], self.buf("moe.sh", M, width))
+        kw = dict(M=M, N=width, i0=top, i1=E, A=y, lda=width, B=x32, ldr=width, p0=ids, p1=wt, ws=pos, C=out, ldc=out.shape[1])
+        if sh is not None:
+            kw["res"] = sh
+        self._op(K_MOE_COMBINE, **kw)
+        return out
+
+    def commit(self):
+        """Close the step: install every carry's next value and advance the slot's position counter by M."""
+        s = self.slot
+        self._op(K_COMMIT, M=max(s.n_commit, 1), i0=self.M, A=s.commit, C=s.pos)
+
+    def finish(self) -> _Plan:
+        self.plan.arr = (Op * len(self.plan.ops))(*self.plan.ops)
+        return self.plan
