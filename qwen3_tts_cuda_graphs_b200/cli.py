@@ -166,6 +166,28 @@ def cmd_http(args):
     server.main(args.rest)
 
 
+def cmd_lm(args):
+    """Token ids in, token ids out, through a sequence model's scheduler (one JSON line per prompt)."""
+    import json
+
+    from .seq_engine import SequenceEngine
+    from .serving import TokenRequest, TokenScheduler
+
+    prompts = [[int(t) for t in p.replace(",", " ").split()] for p in args.tokens]
+    dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype)
+    if dtype is None:
+        raise SystemExit("sequence models run in bf16 or fp32")
+    need = max(len(p) for p in prompts) + args.max_new_tokens
+    eng = SequenceEngine.from_pretrained(args.model, args.device, dtype, max_tokens=max(need, args.max_tokens), max_slots=args.concurrency)
+    sched = TokenScheduler(eng, prefill_chunk=args.prefill_chunk)
+    handles = [sched.submit(TokenRequest(p, args.max_new_tokens, do_sample=not args.greedy, temperature=args.temperature, top_k=args.top_k,
+                                         eos_id=args.eos_id, seed=args.seed)) for p in prompts]
+    sched.run()
+    for h in handles:
+        print(json.dumps({"id": h.id, "tokens": h.generated, "finish": h.reason}))
+    eng.close_all()
+
+
 def build_parser():
     p = argparse.ArgumentParser(prog="faster-qwen3-tts", description="Qwen3-TTS on the fq3 B200 engine")
     p.add_argument("--device", default="cuda", help="Device (cuda)")
@@ -223,6 +245,20 @@ def build_parser():
     sp.add_argument("--output-dir", default="outputs", help="Directory for output wavs")
     sp.add_argument("--concurrency", type=int, default=1, help="utterances decoded in lock-step (continuous batching)")
     sp.set_defaults(fn=cmd_serve)
+
+    sp = sub.add_parser("lm", help="Sequence (language) model: continue prompts given as token ids")
+    sp.add_argument("--model", required=True, help="Directory with config.json (its `architecture` picks the model) and safetensors")
+    sp.add_argument("--tokens", required=True, action="append", help="Prompt as token ids, e.g. '5 17 3'; repeat for more prompts")
+    sp.add_argument("--max-new-tokens", type=int, default=32)
+    sp.add_argument("--temperature", type=float, default=1.0)
+    sp.add_argument("--top-k", type=int, default=0)
+    sp.add_argument("--greedy", action="store_true", help="Disable sampling")
+    sp.add_argument("--eos-id", type=int, default=None)
+    sp.add_argument("--seed", type=int, default=0)
+    sp.add_argument("--prefill-chunk", type=int, default=512, help="Longest prompt portion run in one step")
+    sp.add_argument("--max-tokens", type=int, default=0, help="Positions a state slot holds (default: prompt + new tokens)")
+    sp.add_argument("--concurrency", type=int, default=1, help="State slots: requests alive at once")
+    sp.set_defaults(fn=cmd_lm)
 
     sp = sub.add_parser("http", help="OpenAI-compatible HTTP server (see server.py --help)")
     sp.add_argument("rest", nargs=argparse.REMAINDER)

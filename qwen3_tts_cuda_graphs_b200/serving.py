@@ -522,3 +522,111 @@ class BatchScheduler:
                 h.finish_reason = "error"
                 h.q.put(e)
                 h.q.put(_DONE)
+
+
+# ------------------------------------------------------------------------------------------------
+# Sequence models: token requests over seq_engine.SequenceEngine
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class TokenRequest:
+    tokens: List[int]
+    max_new_tokens: int = 16
+    do_sample: bool = False
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    eos_id: Optional[int] = None
+    seed: int = 0
+
+
+class TokenHandle:
+    def __init__(self, req: TokenRequest, rid: int):
+        self.req, self.id = req, rid
+        self.fed = 0                       # prompt tokens already run
+        self.generated: List[int] = []
+        self.reason: Optional[str] = None  # "eos" | "length" | "capacity"
+        self._done = threading.Event()
+
+    @property
+    def done(self) -> bool:
+        return self._done.is_set()
+
+    def result(self, timeout: Optional[float] = None) -> List[int]:
+        if not self._done.wait(timeout):
+            raise TimeoutError("request still running")
+        return list(self.generated)
+
+
+class TokenScheduler:
+    """Requests wait in a queue, take a free state slot, run their prompt in portions of at most `prefill_chunk` tokens and then
+    decode token by token; the running requests take turns (one step of one request at a time — the engine's step serves one
+    sequence), a finished request gives its slot to the next waiting one.  A request's tokens do not depend on what else is
+    running: every step reads only its own slot.  `run()` drives the loop on the calling thread until everything is done."""
+
+    def __init__(self, engine, prefill_chunk: int = 512):
+        self.engine = engine
+        self.prefill_chunk = max(1, int(prefill_chunk))
+        self.waiting: "queue.Queue[TokenHandle]" = queue.Queue()
+        self.active: List[TokenHandle] = []
+        self._next_id = 0
+        self._logits: Dict[int, torch.Tensor] = {}
+
+    def submit(self, req: TokenRequest) -> TokenHandle:
+        if not req.tokens:
+            raise ValueError("a request needs at least one prompt token")
+        h = TokenHandle(req, self._next_id)
+        self._next_id += 1
+        self.waiting.put(h)
+        return h
+
+    def _admit(self):
+        while self.engine.states.free_slots() > 0 and not self.waiting.empty():
+            h = self.waiting.get()
+            if len(h.req.tokens) + h.req.max_new_tokens > self.engine.states.max_pos:
+                h.reason = "capacity"
+                h._done.set()
+                continue
+            self.engine.open(("sched", h.id))
+            self.active.append(h)
+
+    def _finish(self, h: TokenHandle, reason: str):
+        h.reason = reason
+        self.engine.close(("sched", h.id))
+        self._logits.pop(h.id, None)
+        self.active.remove(h)
+        h._done.set()
+
+    def _advance(self, h: TokenHandle):
+        from .sampling import sample_logits
+
+        r, key = h.req, ("sched", h.id)
+        if h.fed < len(r.tokens):
+            part = r.tokens[h.fed:h.fed + self.prefill_chunk]
+            h.fed += len(part)
+            lg = self.engine.step(key, part, [len(part) - 1] if h.fed == len(r.tokens) else [])
+            if lg is not None:
+                self._logits[h.id] = lg[0].clone()
+            return
+        if r.max_new_tokens <= 0:
+            return self._finish(h, "length")
+        t = int(sample_logits(self._logits[h.id], temperature=r.temperature, top_k=r.top_k, top_p=r.top_p, do_sample=r.do_sample,
+                              seed=r.seed, draw_index=len(h.generated), engine=False))
+        h.generated.append(t)
+        if r.eos_id is not None and t == r.eos_id:
+            return self._finish(h, "eos")
+        if len(h.generated) >= r.max_new_tokens:
+            return self._finish(h, "length")
+        self._logits[h.id] = self.engine.step(key, [t], [0])[0].clone()
+
+    def step(self) -> bool:
+        """One turn for every running request; False when nothing is left to do."""
+        self._admit()
+        if not self.active:
+            return not self.waiting.empty()
+        for h in list(self.active):
+            self._advance(h)
+        return bool(self.active) or not self.waiting.empty()
+
+    def run(self):
+        while self.step():
+            pass
