@@ -54,15 +54,14 @@ def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dic
     latent = rms_unit(h @ W[p + "dkv"].T, eps) * W[p + "dkv.norm"]
     k = (latent @ W[p + "uk"].T).reshape(T, H, dk)
     v = (latent @ W[p + "uv"].T).reshape(T, H, dv)
+    sink = W[p + "sink"] if (p + "sink") in W else None
     out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for i in range(T):
-        for a in range(H):
-            s = (k[: i + 1, a] @ q[i, a]) * m["scale"]
-            sink = W[p + "sink"][a] if (p + "sink") in W else None
-            top = s.max() if sink is None else torch.maximum(s.max(), sink)
-            e = torch.exp(s - top)
-            den = e.sum() + (0.0 if sink is None else torch.exp(sink - top))
-            out[i, a] = (e / den) @ v[: i + 1, a]
+    for i in range(T):                                         # query i sees keys 0..i
+        s = torch.einsum("jhd,hd->hj", k[: i + 1], q[i]) * m["scale"]          # [H, i + 1]
+        top = s.max(-1).values if sink is None else torch.maximum(s.max(-1).values, sink)
+        e = torch.exp(s - top[:, None])
+        den = e.sum(-1) + (0.0 if sink is None else torch.exp(sink - top))     # the sink counts once, has no value
+        out[i] = torch.einsum("hj,jhd->hd", e / den[:, None], v[: i + 1])
     return out.reshape(T, H * dv) @ W[p + "o"].T
 
 

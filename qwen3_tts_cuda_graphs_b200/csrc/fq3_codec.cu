@@ -1158,8 +1158,9 @@ int fq3c_run(const fq3c_op* ops, int n_ops, void* stream) {
       case FQ3C_GEMM: {
         // True 32-bit operands, few rows (decode: weight streaming, one warp per output column) and shapes the tensor-core
         // kernels do not take (K not a multiple of 8, unaligned rows) go to the sequence-model product.
-        if ((o.flags & (FQ3C_F32 | FQ3C_NOROUND)) && o.taps == 1 &&
-            ((o.flags & FQ3C_F32) || o.M <= 4 || o.K % 8 || o.lda % 8 || (reinterpret_cast<uintptr_t>(o.A) & 15) || (reinterpret_cast<uintptr_t>(o.B) & 15))) {
+        if (o.taps == 1 && !(o.flags & ~SEQ_GEMM_FLAGS) && !o.norm_out &&
+            ((o.flags & FQ3C_F32) || ((o.flags & FQ3C_NOROUND) && o.M <= 4) || o.K % 8 || o.lda % 8 ||
+             (reinterpret_cast<uintptr_t>(o.A) & 15) || (reinterpret_cast<uintptr_t>(o.B) & 15))) {
           SeqGemm g{};
           g.A = o.A; g.B = o.B; g.bias = reinterpret_cast<const float*>(o.bias); g.C = o.C;
           g.M = o.M; g.N = o.N; g.K = o.K; g.lda = o.lda; g.ldb = o.K; g.ldc = o.ldc; g.flags = o.flags;

@@ -78,8 +78,7 @@ class SequenceEngine:
             b.plan.keep.append(ids)
             layer_taps = [] if taps else None
             x = self.model.build_step(b, ids, layer_taps)
-            e = {"plan": b.finish(), "ids": ids, "x": x, "taps": layer_taps,
-                 "host_ids": torch.zeros(M, dtype=torch.int32).pin_memory()}
+            e = {"plan": b.finish(), "ids": ids, "x": x, "taps": layer_taps}
             self._steps[key] = e
             while len(self._steps) > self.MAX_PLANS:
                 old_key, old = self._steps.popitem(last=False)
@@ -98,7 +97,7 @@ class SequenceEngine:
             want = torch.zeros(n_want, dtype=torch.int32, device=self.device)
             b.plan.keep.append(want)
             logits = self.model.build_head(b, x, want)
-            e = {"plan": b.finish(), "want": want, "logits": logits, "host_want": torch.zeros(n_want, dtype=torch.int32).pin_memory()}
+            e = {"plan": b.finish(), "want": want, "logits": logits}
             self._heads[key] = e
         return e
 
@@ -108,7 +107,7 @@ class SequenceEngine:
             plan.graph = None
 
     # ---- the step ---------------------------------------------------------------------------------
-    @torch.inference_mode()
+    @torch.no_grad()
     def step(self, request, tokens: Sequence[int], want: Sequence[int] = (), layer_taps: bool = False) -> Optional[torch.Tensor]:
         """Returns logits f32 [len(want), vocab] on the device (a buffer of the cached list: copy it before the next step of the
         same shape), or None when nothing is wanted.  With layer_taps the residual stream after every layer is kept in
@@ -123,20 +122,19 @@ class SequenceEngine:
             raise ValueError("wanted position outside the step")
         self.states.reserve(slot, M)
         e = self._step_plan(slot, M, layer_taps)
-        e["host_ids"].copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
-        e["ids"].copy_(e["host_ids"], non_blocking=True)
+        # from pageable memory: the copy is staged before the call returns, so the host list may change at once
+        e["ids"].copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
         _codec.run_op_plan(self.lib, e["plan"], self.use_graphs)
         self.last_taps = e["taps"]
         if not want:
             return None
         h = self._head_plan(slot, M, layer_taps, len(want), e["x"])
-        h["host_want"].copy_(torch.as_tensor(list(want), dtype=torch.int32))
-        h["want"].copy_(h["host_want"], non_blocking=True)
+        h["want"].copy_(torch.as_tensor(list(want), dtype=torch.int32))
         _codec.run_op_plan(self.lib, h["plan"], self.use_graphs)
         return h["logits"]
 
     # ---- generation ---------------------------------------------------------------------------------
-    @torch.inference_mode()
+    @torch.no_grad()
     def generate(self, tokens: Sequence[int], max_new_tokens: int, *, do_sample: bool = False, temperature: float = 1.0, top_k: int = 0,
                  top_p: float = 1.0, eos_id: Optional[int] = None, seed: int = 0, prefill_chunk: int = 0, request="generate") -> List[int]:
         """Prompt (optionally in portions of `prefill_chunk` tokens), then token-by-token decoding with the framework's sampler."""
