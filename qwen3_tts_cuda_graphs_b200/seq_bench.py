@@ -1,0 +1,252 @@
+"""Throughput of a sequence model at layer sizes that resemble a real model's, beside the closest model of the framework.
+
+`bench.py --seq-model` (the default workload of bench.py is untouched).  Random weights, synthetic tokens.  For each size:
+  * prefill: one step of T prompt tokens through `SequenceEngine.step` (tokens / s), and the same in portions;
+  * decode: single-token steps at context T (tokens / s), replayed as CUDA graphs as the generation path does;
+  * per op kind: device time of every op of the step's list launched alone (CUDA events, L2 flushed before each timed
+    launch), its algorithmic FLOPs and bytes, and the fraction of the roofline max(FLOPs / measured bf16 peak, bytes /
+    measured copy bandwidth) it reaches.
+The closest existing model is the talker (a dense Qwen3 decoder): its dense prefill is an op list on the same library
+(prefill_dense.py), timed op by op the same way, and its decode step is the persistent decode kernel (bytes of weights / time).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import time
+from collections import defaultdict
+
+import torch
+
+from . import codec as K
+from .config import (DenseFFConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SeqLayerConfig, SidalornConfig)
+
+KIND_NAMES = {K.K_GEMM: "gemm (tcgen05 / gemv)", K.K_RMSNORM: "rmsnorm", K.K_ATTN: "attention (prefill, CUDA cores)", 8: "qk-norm + rope + kv",
+              K.K_EMBED: "embed / gather", K.K_TCONV: "time conv", K.K_GNORM: "group norm", K.K_BDGEMM: "block-diagonal product",
+              K.K_LATENT_ATTN: "latent attention", K.K_LRU_SCAN: "lru scan", K.K_POLYNORM: "polynorm", K.K_ROUTER: "router",
+              K.K_MOE_SORT: "moe sort", K.K_GGEMM: "grouped expert product", K.K_MOE_COMBINE: "moe combine", K.K_COMMIT: "state commit"}
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]) * 1e9, float(p["bf16_tflops"]) * 1e12, "measured"
+    except (OSError, KeyError, ValueError):
+        return 6.65e12, 1.59e15, "fallback"
+
+
+def sizes():
+    def model(width, heads, rank, lru_blocks, dense_ff, experts, top, expert_ff, shared_ff, vocab=3072, pairs=2):
+        att = LatentAttentionConfig(heads, 128, 128, rank, 128 ** -0.5)
+        lru = RglruConfig(width, lru_blocks, 4)
+        moe = MoEFFConfig(experts, 2, top, 2, 1, 2.5, expert_ff, shared_ff)
+        layers = []
+        for _ in range(pairs):
+            layers += [SeqLayerConfig("rglru", lru, DenseFFConfig(dense_ff)), SeqLayerConfig("latent_attention", att, moe),
+                       SeqLayerConfig("latent_attention", att, moe)]
+        return SidalornConfig(vocab, width, 1e-6, 2, 4, tuple(layers))
+
+    return {"w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1)}
+
+
+def random_model(cfg: SidalornConfig, device, seed=0):
+    from .sidalorn import SidalornModel, tensor_specs
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    specs = tensor_specs(cfg)
+
+    def get(name):
+        shape = specs[name]
+        if name.endswith(("norm1", "norm2", "final.norm", "dkv.norm")):
+            return torch.ones(shape, device=device)
+        if name.endswith(".act"):
+            return torch.tensor([0.6, 0.3, 0.1, 0.05], device=device)
+        if name.endswith(".lam"):
+            return torch.randn(shape, device=device, generator=g) - 2.0
+        s = 0.3 if name.endswith((".b", ".sink", ".correction", "canon1", ".conv")) else (1.0 if name == "embed" else shape[-1] ** -0.5)
+        return s * torch.randn(shape, device=device, generator=g)
+
+    return SidalornModel(cfg, get, device, f32=False)
+
+
+def op_cost(o, ctx_keys: float):
+    """(FLOPs, bytes) an op has to do / move; element sizes from its flags."""
+    f32 = bool(o.flags & K.F_F32)
+    ws = 4 if f32 else 2
+    outs = 4 if (o.flags & K.F_OUT_F32) else 2
+    k, M, N = o.kind, o.M, o.N
+    if k == K.K_GEMM:
+        return 2.0 * M * N * o.K, (M * o.K + N * o.K) * ws + M * N * outs
+    if k == K.K_BDGEMM:
+        return 2.0 * M * o.i0 * o.i2 * o.cin, o.i0 * o.i2 * o.cin * ws + M * o.i1 * o.cin * 4 + M * N * outs
+    if k == K.K_GGEMM:
+        return 2.0 * M * N * o.K, o.i0 * N * o.K * ws + M * o.K * ws + M * N * outs
+    if k == K.K_LATENT_ATTN:
+        return 4.0 * M * o.i0 * o.i1 * ctx_keys, ctx_keys * o.i1 * ws + 2 * M * N * 4
+    if k == K.K_ATTN:
+        return 4.0 * M * o.i0 * o.i2 * ctx_keys, M * (o.i0 + 2 * o.i1) * o.i2 * 2 + M * o.i0 * o.i2 * 2
+    if k == K.K_LRU_SCAN:
+        return 0.0, M * N * (4 * 4 + outs)
+    if k == K.K_COMMIT:
+        return 0.0, 0.0
+    if k in (K.K_ROUTER, K.K_MOE_SORT):
+        return 0.0, M * max(N, o.i0) * 8
+    if k == K.K_MOE_COMBINE:
+        return 0.0, M * N * 4 * (o.i0 + 2)
+    return 0.0, M * max(N, 1) * (4 + outs)
+
+
+def time_ops(lib, arr, n_ops, ctx_of, skip_last=False, reps=5):
+    """Every op launched alone: median device time (ms) of `reps` launches, L2 flushed before each."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    hbm, tflops, _ = peaks()
+    by_kind = defaultdict(lambda: [0.0, 0.0, 0])
+    n = n_ops - (1 if skip_last else 0)
+    for i in range(n):
+        one = (K.Op * 1)(arr[i])
+        ts = []
+        for r in range(reps + 1):
+            flush.fill_(r)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            if lib.fq3c_run(one, 1, stream) != 0:
+                raise RuntimeError(lib.fq3c_last_error().decode())
+            b.record()
+            torch.cuda.synchronize()
+            if r:
+                ts.append(a.elapsed_time(b))
+        ms = sorted(ts)[len(ts) // 2]
+        fl, by = op_cost(arr[i], ctx_of(arr[i]))
+        roof_ms = max(fl / tflops, by / hbm) * 1e3
+        e = by_kind[arr[i].kind]
+        e[0] += ms
+        e[1] += roof_ms
+        e[2] += 1
+    return {KIND_NAMES.get(k, str(k)): {"ms": round(v[0], 4), "roofline_ms": round(v[1], 4), "frac": round(v[1] / v[0], 4) if v[0] else None, "ops": v[2]}
+            for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1][0])}
+
+
+def timed(fn, warmup=3, reps=5, flush=None):
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for r in range(reps):
+        if flush is not None:
+            flush.fill_(r)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def bench_sidalorn(name, cfg, T, device):
+    from .seq_engine import SequenceEngine
+
+    model = random_model(cfg, device)
+    eng = SequenceEngine(model, T + 64, 1)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (T + 40,), generator=g).tolist()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = {"model": f"Sidalorn {name}", "width": cfg.width, "layers": len(cfg.layers), "T": T}
+
+    def prefill(portion):
+        def run():
+            eng.close("p")
+            for lo in range(0, T, portion):
+                eng.step("p", toks[lo:lo + portion], [portion - 1] if lo + portion >= T else [])
+        return run
+
+    ms = timed(prefill(T), flush=flush)
+    out["prefill_ms"], out["prefill_tok_s"] = round(ms, 3), round(T / ms * 1e3)
+    ms = timed(prefill(512), flush=flush)
+    out["prefill_512_portions_ms"], out["prefill_512_portions_tok_s"] = round(ms, 3), round(T / ms * 1e3)
+    # decode at context T: 32 single-token steps per timed run (the slot holds T + 64 positions)
+    prefill(T)()
+    base = eng.states.get("p").length
+
+    def decode():
+        slot = eng.states.get("p")
+        slot.length = base
+        slot.pos.fill_(base)
+        for i in range(32):
+            eng.step("p", [toks[T + i]], [0])
+    ms = timed(decode, flush=flush)
+    out["decode_ms_per_token"], out["decode_tok_s"] = round(ms / 32, 4), round(32 / ms * 1e3)
+    # weights a decode step streams: everything but the unchosen experts and the embedding table's other rows
+    wb = 0
+    for i, (L, w) in enumerate(zip(cfg.layers, model.layers)):
+        for k, t in w["mix"].items():
+            wb += t.numel() * t.element_size() if t is not None else 0
+        f = w.get("ff")
+        if f:
+            if isinstance(L.mlp, MoEFFConfig):
+                per = f["up"][0].numel() * 2 * 2
+                wb += per * min(L.mlp.top, L.mlp.experts) + f["router"].numel() * 4
+                wb += sum(f[k].numel() * 2 for k in ("shared_up", "shared_down") if f[k] is not None)
+            else:
+                wb += sum(f[k].numel() * f[k].element_size() for k in ("up", "down"))
+    wb += model.g["head"].numel() * 2
+    hbm, _, how = peaks()
+    out["decode_weight_bytes"] = wb
+    out["decode_hbm_frac"] = round(wb / (ms / 32 * 1e-3) / hbm, 4)
+    out["peaks"] = how
+    # op by op
+    slot = eng.states.get("p")
+    slot.length = 0
+    slot.pos.zero_()
+    e = eng._step_plan(slot, T)
+    out["prefill_ops"] = time_ops(eng.lib, e["plan"].arr, len(e["plan"].ops), lambda o: (T + 1) / 2.0, skip_last=True)
+    slot.pos.fill_(T)
+    e1 = eng._step_plan(slot, 1)
+    out["decode_ops"] = time_ops(eng.lib, e1["plan"].arr, len(e1["plan"].ops), lambda o: float(T + 1), skip_last=True)
+    eng.close_all()
+    return out
+
+
+def bench_talker(T, device, preset="0.6B-Base"):
+    """The closest existing model: dense prefill op list (rows [0, T - 1)) and the decode kernel's talker step."""
+    from . import FasterQwen3TTS
+    from .engine import SamplingPolicy
+    from .weights import param_bytes
+
+    tts = FasterQwen3TTS.from_pretrained(f"synthetic://{preset}", device=device, dtype=torch.bfloat16, attn_implementation="eager",
+                                         max_seq_len=max(2048, T + 64), seed=0)
+    eng = tts.model.engine
+    cfg = tts.model.cfg if hasattr(tts.model, "cfg") else None
+    H = eng.cfg.talker.hidden_size
+    x = (0.5 * torch.randn(T, H, device=device)).to(torch.bfloat16)
+    pol = SamplingPolicy(do_sample=False, repetition_penalty=1.0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = {"model": f"talker {preset}", "width": H, "layers": eng.cfg.talker.num_hidden_layers, "T": T}
+    ms = timed(lambda: eng.prefill(0, x, 0, pol, dense=True), flush=flush)
+    out["prefill_ms"], out["prefill_tok_s"] = round(ms, 3), round(T / ms * 1e3)
+    row = x[0].contiguous()
+    ms = timed(lambda: eng.talker_step(0, row, T, want_logits=False), reps=9, flush=flush)
+    pb = param_bytes(eng.cfg)["talker_step"]
+    hbm, _, how = peaks()
+    out["decode_ms_per_token"], out["decode_tok_s"] = round(ms, 4), round(1e3 / ms)
+    out["decode_weight_bytes"], out["decode_hbm_frac"], out["peaks"] = pb, round(pb / (ms * 1e-3) / hbm, 4), how
+    d = eng._dense
+    if d is not None:
+        out["prefill_ops"] = time_ops(d.lib, d.arr, len(d.ops), lambda o: (T + 1) / 2.0)
+    return out
+
+
+def main(T: int = 2048, which: str = "w1024,w2048"):
+    device = "cuda"
+    res = {"bench": "sequence model beside the closest existing model", "data": "synthetic", "dtype": "bf16", "rows": []}
+    all_sizes = sizes()
+    for name in which.split(","):
+        res["rows"].append(bench_sidalorn(name, all_sizes[name], T, device))
+        torch.cuda.empty_cache()
+    res["rows"].append(bench_talker(T, device))
+    print(json.dumps(res))
+    return res
