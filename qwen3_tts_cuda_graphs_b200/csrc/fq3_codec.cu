@@ -1099,6 +1099,35 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       if (o.i0 < 1 || o.i1 < 1 || !o.A || !o.B || !o.C) return fail("latent_attn: missing operand");
       const int splits = std::max(1, o.K);
       if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.i1 + 2) * 4)) return fail("latent_attn: workspace too small for the splits");
+      // bf16 cache with a rank the MMA tiles divide: the tensor-core kernel (FQ3S_ATTN_MMA=0: CUDA cores everywhere)
+      static int use_mma = -1;
+      if (use_mma < 0) { const char* e6 = getenv("FQ3S_ATTN_MMA"); use_mma = (e6 == nullptr || atoi(e6) != 0) ? 1 : 0; }
+      const int RS = (o.i1 + 255) / 256;
+      if (use_mma && !(o.flags & FQ3C_F32) && RS <= 2 && o.i1 % 16 == 0 && o.i1 % (8 * RS) == 0 && o.ldr % 8 == 0 &&
+          !(reinterpret_cast<uintptr_t>(o.B) & 15)) {
+        const int TJ = o.i1 > 256 ? 32 : 64;
+        const size_t smem = (size_t)(LM_QB * 16 + TJ) * (o.i1 + 8) * 2;
+        const int nt_o = (o.i1 / RS) / 8;
+        static bool mattr[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !mattr[dev]) {
+          cudaFuncSetAttribute(fq3s_latent_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          cudaFuncSetAttribute(fq3s_latent_attn_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          cudaFuncSetAttribute(fq3s_latent_attn_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          mattr[dev] = true;
+        }
+        dim3 grid((o.M + LM_QB - 1) / LM_QB, (o.i0 + 15) / 16, splits);
+        const int nth = 32 * LM_QB * RS;
+        if (nt_o <= 8) fq3s_latent_attn_mma_kernel<8><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
+        else if (nt_o <= 16) fq3s_latent_attn_mma_kernel<16><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
+        else fq3s_latent_attn_mma_kernel<32><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
+        if (splits > 1) {
+          fq3s_latent_merge_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o, splits);
+          count_launches(1);
+        }
+        return 0;
+      }
       int HG = std::max(1, std::min(o.i0, o.i2 > 0 ? o.i2 : o.i0));
       while (HG > 1 && latent_attn_smem(HG, o.i1) > 160 * 1024) --HG;
       const size_t smem = latent_attn_smem(HG, o.i1);

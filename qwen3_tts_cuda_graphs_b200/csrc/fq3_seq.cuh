@@ -655,3 +655,169 @@ __global__ void __launch_bounds__(128) fq3s_latent_merge_kernel(const fq3c_op o,
     c[r] = acc / den;
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Latent attention on the tensor cores (bf16 cache).  The heads are the M dimension of the MMA: one query's 16 heads share every
+// latent row, so scores S [16 heads x TJ keys] = Q' [16 x R] . C^T and outputs O' [16 x R] += P [16 x TJ] . C [TJ x R] are
+// m16n8k16 tiles whose B operand is the staged tile of latent rows itself (row-major for the scores, ldmatrix.trans for the
+// outputs).  A block takes QB = 4 consecutive queries (they see almost the same keys) x RS slices of R (<= 256 columns of O' per
+// warp: 128 accumulator registers); the RS warps of a query compute its scores redundantly.  Scores, maxima, sums and the
+// rescaling are f32; a weight enters the output product as a bf16 pair p_hi + p_lo (two MMAs), i.e. with 16 mantissa bits, the
+// query as one bf16 (the rounding a bf16 product applies to its operand).  grid (ceil(M / 4), ceil(H / 16), splits).
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int LM_QB = 4;
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <int NTM>
+__global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op o, const int RS, const int splits, const int TJ) {
+  extern __shared__ __align__(16) unsigned char lm_raw[];
+  const int R = o.i1, H = o.i0, LDQ = R + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(lm_raw);          // [QB][16][LDQ]
+  bf16* Ct = Qs + (size_t)LM_QB * 16 * LDQ;            // [TJ][LDQ]
+  const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wq = warp / RS, wr = warp - wq * RS;
+  const int m0 = blockIdx.x * LM_QB, h0 = blockIdx.y * 16, z = blockIdx.z;
+  const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
+  const int nk_max = P + min(o.M, m0 + LM_QB);
+  int per = (nk_max + splits - 1) / splits;
+  per = (per + TJ - 1) / TJ * TJ;
+  const int j0 = z * per, j1 = min(nk_max, j0 + per);
+  const int m = m0 + wq;
+  const bool active = m < o.M;
+  const int nk = min(P + m + 1, j1);                   // this query's keys end here (inside this split)
+  const float* A = reinterpret_cast<const float*>(o.A);
+  for (int i = tid; i < LM_QB * 16 * R; i += nth) {
+    const int q = i / (16 * R), rem = i - q * 16 * R, h = rem / R, r = rem - h * R;
+    const int mm = m0 + q;
+    const float v = (mm < o.M && h0 + h < H) ? A[(size_t)mm * o.lda + (size_t)(h0 + h) * R + r] * o.f0 : 0.f;
+    Qs[(q * 16 + h) * LDQ + r] = __float2bfloat16_rn(v);
+  }
+  float oacc[NTM][4];
+#pragma unroll
+  for (int i = 0; i < NTM; ++i) { oacc[i][0] = 0.f; oacc[i][1] = 0.f; oacc[i][2] = 0.f; oacc[i][3] = 0.f; }
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  const int cw = R / RS, nt_o = cw >> 3, c0 = wr * cw;
+  const bf16* cache = reinterpret_cast<const bf16*>(o.B);
+  const int chunks = R >> 3;
+  const bf16* Qw = Qs + (size_t)wq * 16 * LDQ;
+  __syncthreads();
+  for (int jt = j0; jt < j1; jt += TJ) {
+    for (int i = tid; i < TJ * chunks; i += nth) {
+      const int row = i / chunks, c = i - row * chunks;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (jt + row < j1) v = *reinterpret_cast<const uint4*>(cache + (size_t)(jt + row) * o.ldr + c * 8);
+      *reinterpret_cast<uint4*>(Ct + (size_t)row * LDQ + c * 8) = v;
+    }
+    __syncthreads();
+    if (active && jt < nk) {
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+      for (int kk = 0; kk < R; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(Qw + g * LDQ + kk + t * 2);
+        a[1] = *reinterpret_cast<const uint32_t*>(Qw + (g + 8) * LDQ + kk + t * 2);
+        a[2] = *reinterpret_cast<const uint32_t*>(Qw + g * LDQ + kk + 8 + t * 2);
+        a[3] = *reinterpret_cast<const uint32_t*>(Qw + (g + 8) * LDQ + kk + 8 + t * 2);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          if (nt * 8 < TJ) {
+            const bf16* bp = Ct + (size_t)(nt * 8 + g) * LDQ + kk + t * 2;
+            mma16816(s[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+          }
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int key = jt + nt * 8 + t * 2;
+        const bool v0 = (nt * 8 < TJ) && key < nk, v1 = (nt * 8 < TJ) && key + 1 < nk;
+        if (!v0) { s[nt][0] = -INFINITY; s[nt][2] = -INFINITY; }
+        if (!v1) { s[nt][1] = -INFINITY; s[nt][3] = -INFINITY; }
+        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(mrow[0], mx0), mn1 = fmaxf(mrow[1], mx1);
+      const float u0 = mn0 == -INFINITY ? 0.f : mn0, u1 = mn1 == -INFINITY ? 0.f : mn1;
+      const float al0 = mrow[0] == -INFINITY ? 0.f : expf(mrow[0] - u0), al1 = mrow[1] == -INFINITY ? 0.f : expf(mrow[1] - u1);
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = expf(s[nt][0] - u0); s[nt][1] = expf(s[nt][1] - u0);
+        s[nt][2] = expf(s[nt][2] - u1); s[nt][3] = expf(s[nt][3] - u1);
+        sum0 += s[nt][0] + s[nt][1];
+        sum1 += s[nt][2] + s[nt][3];
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      lrow[0] = lrow[0] * al0 + sum0; lrow[1] = lrow[1] * al1 + sum1;
+      mrow[0] = mn0; mrow[1] = mn1;
+#pragma unroll
+      for (int nt = 0; nt < NTM; ++nt) { oacc[nt][0] *= al0; oacc[nt][1] *= al0; oacc[nt][2] *= al1; oacc[nt][3] *= al1; }
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        if (ks * 16 < TJ) {
+          uint32_t ah[4], al[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float p0 = s[2 * ks + (q >> 1)][(q & 1) * 2], p1 = s[2 * ks + (q >> 1)][(q & 1) * 2 + 1];
+            const float h0f = bf16r(p0), h1f = bf16r(p1);
+            ah[q] = pack_bf16(h0f, h1f);
+            al[q] = pack_bf16(p0 - h0f, p1 - h1f);
+          }
+          const int mi = lane >> 3;
+          const bf16* base = Ct + (size_t)(ks * 16 + (mi & 1) * 8 + (lane & 7)) * LDQ + c0 + (mi >> 1) * 8;
+#pragma unroll
+          for (int nt = 0; nt < NTM; nt += 2) {
+            if (nt < nt_o) {
+              uint32_t b[4];
+              ldmatrix_x4_trans(b, base + nt * 8);
+              mma16816(oacc[nt], ah, b[0], b[1]);
+              mma16816(oacc[nt], al, b[0], b[1]);
+              if (nt + 1 < nt_o) {
+                mma16816(oacc[nt + 1], ah, b[2], b[3]);
+                mma16816(oacc[nt + 1], al, b[2], b[3]);
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!active) return;
+  const float* sink = reinterpret_cast<const float*>(o.scale);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int h = h0 + g + half * 8;
+    if (h >= H) continue;
+    const float mr = mrow[half], lr = lrow[half];
+    if (splits == 1) {
+      float f = 1.f, den = lr;
+      if (sink) {
+        const float mm = fmaxf(mr, sink[h]);
+        f = mr == -INFINITY ? 0.f : expf(mr - mm);
+        den = lr * f + expf(sink[h] - mm);
+      }
+      const float sc = f / den;
+      float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h * R + c0;
+#pragma unroll
+      for (int nt = 0; nt < NTM; ++nt)
+        if (nt < nt_o) { c[nt * 8 + t * 2] = oacc[nt][half * 2] * sc; c[nt * 8 + t * 2 + 1] = oacc[nt][half * 2 + 1] * sc; }
+    } else {
+      float* dst = reinterpret_cast<float*>(o.ws) + (((size_t)m * H + h) * splits + z) * (R + 2);
+      if (wr == 0 && t == 0) { dst[0] = mr; dst[1] = lr; }
+#pragma unroll
+      for (int nt = 0; nt < NTM; ++nt)
+        if (nt < nt_o) { dst[2 + c0 + nt * 8 + t * 2] = oacc[nt][half * 2]; dst[2 + c0 + nt * 8 + t * 2 + 1] = oacc[nt][half * 2 + 1]; }
+    }
+  }
+}

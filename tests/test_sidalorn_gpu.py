@@ -166,6 +166,37 @@ def test_latent_attention_alone(sink, f32):
         assert float((no_sink - want).abs().max() / want.abs().max()) > 0.3
 
 
+@pytest.mark.parametrize("H,R", [(3, 48), (18, 80), (5, 128), (2, 256), (17, 336)])
+def test_latent_attention_tensor_core_tiles(H, R):
+    """bf16 cache with a rank the MMA tiles divide: every accumulator width of the tensor-core kernel, one and two column slices
+    per query, an odd tile count per slice, head counts on both sides of a 16-head block; portions that cross its 64- and 32-key
+    tiles, its 4-query blocks and its key-range splits, and single decoded tokens.  Peaky queries: one key off shows."""
+    from qwen3_tts_cuda_graphs_b200.config import LatentAttentionConfig
+    from qwen3_tts_cuda_graphs_b200.seq_state import StateSpec
+
+    dk, dv, width, T = 16, 8, 64, 209
+    W = _attn_weights(H, dk, dv, R, width, "random", seed=5, peaky=4.0)
+    m = {"heads": H, "dim": dk, "vdim": dv, "kv_rank": R, "scale": 0.3}
+    h = torch.randn(T, width, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).float()
+    want = so.latent_attention(h.to(F64), {"m." + k: v.to(F64) for k, v in W.items()}, "m.", m, 1e-6)
+    wdt = torch.bfloat16
+    pw = {"wqd": cuda(torch.cat([W["q"], W["dkv"]]), wdt), "dkv_norm": cuda(W["dkv.norm"]),
+          "uk_t": cuda(W["uk"].reshape(H, dk, R).transpose(1, 2), wdt), "uv": cuda(W["uv"].reshape(H, dv, R), wdt),
+          "sink": cuda(W["sink"]), "o": cuda(W["o"], wdt)}
+    bench = Bench([StateSpec("lat", "append", R, dtype=wdt)], f32=False)
+    rows, at = [], 0
+    for n in (70, 1, 1, 2, 5, 50, 1, 3, 67, 9):
+        part = cuda(h[at:at + n], wdt)
+        out = torch.zeros(n, width, device="cuda")
+        bench.run(n, lambda b: b.latent_attention(part, LatentAttentionConfig(H, dk, dv, R, 0.3), pw, "lat", 1e-6, out))
+        rows.append(out.cpu())
+        at += n
+    assert at == T
+    got = torch.cat(rows).to(F64)
+    err = (got - want).abs().amax(-1) / want.abs().max()
+    assert float(err.max()) < 3e-2, (float(err.max()), int(err.argmax()))
+
+
 @pytest.mark.parametrize("blocks,conv,T", [(3, 4, 40), (1, 1, 9), (2, 2, 600)])
 def test_rglru_alone(blocks, conv, T):
     from qwen3_tts_cuda_graphs_b200.config import RglruConfig
