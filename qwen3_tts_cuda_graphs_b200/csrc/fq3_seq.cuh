@@ -126,7 +126,41 @@ __global__ void __launch_bounds__(256) fq3s_gemm_kernel(const SeqGemm g) {
 
 // Same contract on the bf16 tensor cores (mma.sync m16n8k16, f32 accumulate) for bf16 weights: the block-diagonal and grouped
 // products of real-size layers.  64 x 64 x 32 tiles, four warps, each a 32 x 32 quadrant.  A may be f32 (rounded to bf16 as it is
-// staged, which is what a bf16 product does to its operand) and rows may be gathered.
+// staged, which is what a bf16 product does to its operand) and rows may be gathered.  Every thread stages 16 consecutive k of
+// one A row and one B row: with 16-byte loads where the operand's rows allow it (`vec`), element by element otherwise and at
+// the ragged end of K; the next tile's values are fetched into registers before the current tile's MMAs run.
+template <typename T>
+__device__ __forceinline__ void sg_fetch16(const T* p, const bool vec, const int kleft, uint4 (&r)[2]) {
+  // p: the row's element at this thread's first k, or nullptr for a row outside the tile; kleft: valid elements from there on
+  if (p == nullptr || kleft <= 0) { r[0] = make_uint4(0u, 0u, 0u, 0u); r[1] = r[0]; return; }
+  if (vec && kleft >= 16) {
+    if (sizeof(T) == 2) {
+      r[0] = *reinterpret_cast<const uint4*>(p);
+      r[1] = *reinterpret_cast<const uint4*>(p + 8);
+    } else {
+      uint32_t u[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + 4 * q);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+        u[2 * q] = *reinterpret_cast<const uint32_t*>(&lo);
+        u[2 * q + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+      r[0] = make_uint4(u[0], u[1], u[2], u[3]);
+      r[1] = make_uint4(u[4], u[5], u[6], u[7]);
+    }
+    return;
+  }
+  uint32_t u[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float a = 2 * q < kleft ? ldf<T>(p + 2 * q) : 0.f, b = 2 * q + 1 < kleft ? ldf<T>(p + 2 * q + 1) : 0.f;
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    u[q] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  r[0] = make_uint4(u[0], u[1], u[2], u[3]);
+  r[1] = make_uint4(u[4], u[5], u[6], u[7]);
+}
 template <typename TA>
 __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
   constexpr int LD = 32 + 8;
@@ -154,9 +188,13 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
   // loaders: thread -> (row = tid / 2, 16 consecutive k)
   const int lr = tid >> 1, lk = (tid & 1) * 16;
   const int ar = row0 + lr;
-  long long a_row = -1;
-  if (ar < row_end) a_row = g.rows ? g.rows[ar] : ar;
+  const TA* a_ptr = nullptr;
+  if (ar < row_end) a_ptr = Ap + (size_t)(g.rows ? g.rows[ar] : ar) * g.lda + lk;
   const int bn = col0 + lr;
+  const bf16* b_ptr = bn < g.N ? Bp + (size_t)bn * g.ldb + lk : nullptr;
+  constexpr int AV = 16 / sizeof(TA);   // elements per 16 bytes
+  const bool vec_a = (g.lda % AV == 0) && ((reinterpret_cast<uintptr_t>(Ap) & 15) == 0);
+  const bool vec_b = (g.ldb % 8 == 0) && ((reinterpret_cast<uintptr_t>(Bp) & 15) == 0);
   const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
   float acc[2][4][4];
 #pragma unroll
@@ -165,14 +203,19 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  uint4 ra[2], rb[2];
+  sg_fetch16<TA>(a_ptr, vec_a, g.K - lk, ra);
+  sg_fetch16<bf16>(b_ptr, vec_b, g.K - lk, rb);
   for (int k0 = 0; k0 < g.K; k0 += 32) {
-#pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const int k = k0 + lk + q;
-      As[lr * LD + lk + q] = (a_row >= 0 && k < g.K) ? __float2bfloat16_rn(ldf<TA>(Ap + (size_t)a_row * g.lda + k)) : __float2bfloat16_rn(0.f);
-      Bs[lr * LD + lk + q] = (bn < g.N && k < g.K) ? Bp[(size_t)bn * g.ldb + k] : __float2bfloat16_rn(0.f);
-    }
+    *reinterpret_cast<uint4*>(&As[lr * LD + lk]) = ra[0];
+    *reinterpret_cast<uint4*>(&As[lr * LD + lk + 8]) = ra[1];
+    *reinterpret_cast<uint4*>(&Bs[lr * LD + lk]) = rb[0];
+    *reinterpret_cast<uint4*>(&Bs[lr * LD + lk + 8]) = rb[1];
     __syncthreads();
+    if (k0 + 32 < g.K) {
+      sg_fetch16<TA>(a_ptr ? a_ptr + k0 + 32 : nullptr, vec_a, g.K - (k0 + 32 + lk), ra);
+      sg_fetch16<bf16>(b_ptr ? b_ptr + k0 + 32 : nullptr, vec_b, g.K - (k0 + 32 + lk), rb);
+    }
 #pragma unroll
     for (int kk = 0; kk < 32; kk += 16) {
       uint32_t a[2][4], b[4][2];

@@ -99,12 +99,13 @@ def op_cost(o, ctx_keys: float):
     return 0.0, M * max(N, 1) * (4 + outs)
 
 
-def time_ops(lib, arr, n_ops, ctx_of, skip_last=False, reps=5):
+def time_ops(lib, arr, n_ops, ctx_of, skip_last=False, reps=5, top=None):
     """Every op launched alone: median device time (ms) of `reps` launches, L2 flushed before each."""
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
     hbm, tflops, _ = peaks()
     by_kind = defaultdict(lambda: [0.0, 0.0, 0])
+    single = []
     n = n_ops - (1 if skip_last else 0)
     for i in range(n):
         one = (K.Op * 1)(arr[i])
@@ -126,6 +127,10 @@ def time_ops(lib, arr, n_ops, ctx_of, skip_last=False, reps=5):
         e[0] += ms
         e[1] += roof_ms
         e[2] += 1
+        single.append({"op": KIND_NAMES.get(arr[i].kind, str(arr[i].kind)), "M": arr[i].M, "N": arr[i].N, "K": arr[i].K, "ms": round(ms, 4),
+                       "roofline_ms": round(roof_ms, 4), "frac": round(roof_ms / ms, 4) if ms else None})
+    if top is not None:
+        top.extend(sorted(single, key=lambda d: -d["ms"])[:8])
     return {KIND_NAMES.get(k, str(k)): {"ms": round(v[0], 4), "roofline_ms": round(v[1], 4), "frac": round(v[1] / v[0], 4) if v[0] else None, "ops": v[2]}
             for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1][0])}
 
@@ -203,7 +208,8 @@ def bench_sidalorn(name, cfg, T, device):
     slot.length = 0
     slot.pos.zero_()
     e = eng._step_plan(slot, T)
-    out["prefill_ops"] = time_ops(eng.lib, e["plan"].arr, len(e["plan"].ops), lambda o: (T + 1) / 2.0, skip_last=True)
+    out["prefill_slowest"] = []
+    out["prefill_ops"] = time_ops(eng.lib, e["plan"].arr, len(e["plan"].ops), lambda o: (T + 1) / 2.0, skip_last=True, top=out["prefill_slowest"])
     slot.pos.fill_(T)
     e1 = eng._step_plan(slot, 1)
     out["decode_ops"] = time_ops(eng.lib, e1["plan"].arr, len(e1["plan"].ops), lambda o: float(T + 1), skip_last=True)
@@ -236,7 +242,8 @@ def bench_talker(T, device, preset="0.6B-Base"):
     out["decode_weight_bytes"], out["decode_hbm_frac"], out["peaks"] = pb, round(pb / (ms * 1e-3) / hbm, 4), how
     d = eng._dense
     if d is not None:
-        out["prefill_ops"] = time_ops(d.lib, d.arr, len(d.ops), lambda o: (T + 1) / 2.0)
+        out["prefill_slowest"] = []
+        out["prefill_ops"] = time_ops(d.lib, d.arr, len(d.ops), lambda o: (T + 1) / 2.0, top=out["prefill_slowest"])
     return out
 
 
