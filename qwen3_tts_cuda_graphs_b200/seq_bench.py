@@ -194,7 +194,7 @@ def bench_sidalorn(name, cfg, T, device):
         if f:
             if isinstance(L.mlp, MoEFFConfig):
                 per = f["up"][0].numel() * 2 * 2
-                wb += per * min(L.mlp.top, L.mlp.experts) + f["router"].numel() * 4
+                wb += per * min(L.mlp.top, L.mlp.experts) + f["router"].numel() * f["router"].element_size()
                 wb += sum(f[k].numel() * 2 for k in ("shared_up", "shared_down") if f[k] is not None)
             else:
                 wb += sum(f[k].numel() * f[k].element_size() for k in ("up", "down"))

@@ -175,11 +175,13 @@ class StepBuilder:
         return self.linear(za, w["down"], out)
 
     def moe_ff(self, x32: torch.Tensor, xop: torch.Tensor, c: MoEFFConfig, w: dict, out: torch.Tensor):
-        """x32: the f32 rows (router input, identity experts); xop: the same rows as product operands.  w: router f32 [n, width],
-        correction f32 [n] or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None."""
+        """x32: the f32 rows (identity experts); xop: the same rows as product operands.  w: router [n, width], correction f32 [n]
+        or None, up [E, ff, width], down [E, width, ff], shared_up / shared_down or None.  The router's logits are f32 either way:
+        f32 router weights take the f32 rows (true 32-bit product); bf16 ones take the bf16 rows, whose products with the weights
+        are exact in f32 and are summed in f32."""
         M, n, top, E = self.M, c.routed, c.top, c.experts
         width = x32.shape[1]
-        z = self.linear(x32, w["router"], self.buf("moe.z", M, n))
+        z = self.linear(x32 if w["router"].dtype == torch.float32 else xop, w["router"], self.buf("moe.z", M, n))
         ids = self.buf("moe.ids", M, top, torch.int32)
         wt = self.buf("moe.w", M, top)
         kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt)

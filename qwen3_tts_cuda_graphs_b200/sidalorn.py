@@ -137,7 +137,7 @@ class SidalornModel:
                 if isinstance(f, DenseFFConfig):
                     d["ff"] = {"up": W(raw(p + "mlp.up")), "down": W(raw(p + "mlp.down")), "act": F(raw(p + "mlp.act"))}
                 else:
-                    d["ff"] = {"router": F(raw(p + "mlp.router")), "correction": F(raw(p + "mlp.correction")),
+                    d["ff"] = {"router": W(raw(p + "mlp.router")), "correction": F(raw(p + "mlp.correction")),
                                "up": W(torch.stack([raw(p + f"mlp.e{e}.up") for e in range(f.experts)])),
                                "down": W(torch.stack([raw(p + f"mlp.e{e}.down") for e in range(f.experts)])),
                                "shared_up": W(raw(p + "mlp.shared.up")) if f.shared_ff else None,
