@@ -1011,6 +1011,23 @@ int launch_seq_gemm(const SeqGemm& g, bool a_f32, bool b_f32, bool exact, int zc
     else fq3s_gemv_kernel<bf16, bf16><<<grid, 256, gemv_smem, s>>>(g);
     return 0;
   }
+  if (g.seg && zcount == 1 && g.M <= 16 && (size_t)g.K * sizeof(float) <= 96 * 1024) {
+    static bool gattr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !gattr[dev]) {
+      cudaFuncSetAttribute(fq3s_ggemv_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(fq3s_ggemv_kernel<float, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaFuncSetAttribute(fq3s_ggemv_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      gattr[dev] = true;
+    }
+    dim3 grid((g.N + 7) / 8, g.M, 1);
+    const size_t smem = (size_t)g.K * sizeof(float);
+    if (b_f32) fq3s_ggemv_kernel<float, float><<<grid, 256, smem, s>>>(g);
+    else if (a_f32) fq3s_ggemv_kernel<float, bf16><<<grid, 256, smem, s>>>(g);
+    else fq3s_ggemv_kernel<bf16, bf16><<<grid, 256, smem, s>>>(g);
+    return 0;
+  }
   dim3 grid((g.N + 63) / 64, row_tiles, zcount);
   if (b_f32) fq3s_gemm_kernel<float, float><<<grid, 256, 0, s>>>(g);
   else if (a_f32 && exact) fq3s_gemm_kernel<float, bf16><<<grid, 256, 0, s>>>(g);
@@ -1106,7 +1123,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       if (use_mma && !(o.flags & FQ3C_F32) && RS <= 2 && o.i1 % 16 == 0 && o.i1 % (8 * RS) == 0 && o.ldr % 8 == 0 &&
           !(reinterpret_cast<uintptr_t>(o.B) & 15)) {
         const int TJ = o.i1 > 256 ? 32 : 64;
-        const size_t smem = (size_t)(LM_QB * 16 + TJ) * (o.i1 + 8) * 2;
+        const size_t smem = (size_t)(LM_QB * 16 + 2 * TJ) * (o.i1 + 8) * 2;   // queries + two key tiles
         const int nt_o = (o.i1 / RS) / 8;
         static bool mattr[64] = {};
         int dev = 0;

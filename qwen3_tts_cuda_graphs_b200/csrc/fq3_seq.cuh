@@ -326,6 +326,54 @@ __global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
   }
 }
 
+// Grouped product with few rows in flight (decode: tokens x chosen experts <= 16 rows): block (column octet, sorted row); the row's
+// expert comes from the segment starts, a warp per output column streams that expert's weight row once with 16-byte loads.
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(256) fq3s_ggemv_kernel(const SeqGemm g) {
+  extern __shared__ float xs[];  // [K]
+  const int p = blockIdx.y;
+  int e = 0;
+  while (e < g.E && p >= g.seg[e + 1]) ++e;
+  if (e >= g.E) return;          // beyond the last segment: choices without tensors (identity experts) leave fewer rows
+  const int arow = g.rows ? g.rows[p] : p;
+  const TA* a = reinterpret_cast<const TA*>(g.A) + (size_t)arow * g.lda;
+  for (int i = threadIdx.x; i < g.K; i += blockDim.x) xs[i] = ldf<TA>(a + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= g.N) return;
+  const TB* w = reinterpret_cast<const TB*>(g.B) + (size_t)e * g.b_estride + (size_t)n * g.ldb;
+  float acc = 0.f;
+  constexpr int VEC = 16 / sizeof(TB);
+  if (((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (g.K % VEC == 0)) {
+    for (int k = lane * VEC; k < g.K; k += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+      if (sizeof(TB) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc = fmaf(__uint_as_float(u[q] << 16), xs[k + 2 * q], acc);
+          acc = fmaf(__uint_as_float(u[q] & 0xffff0000u), xs[k + 2 * q + 1], acc);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc = fmaf(__uint_as_float(u[q]), xs[k + q], acc);
+      }
+    }
+  } else {
+    for (int k = lane; k < g.K; k += 32) acc = fmaf(ldf<TB>(w + k), xs[k], acc);
+  }
+  float v = warp_sum(acc);
+  if (lane == 0) {
+    if (g.flags & FQ3C_GELU) v = gelu_f(v);
+    if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
+    if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+    const size_t ci = (size_t)p * g.ldc + n;
+    if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+    else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename TB>
 __global__ void fq3s_embed_kernel(const fq3c_op o) {
@@ -722,10 +770,11 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   extern __shared__ __align__(16) unsigned char lm_raw[];
   const int R = o.i1, H = o.i0, LDQ = R + 8;
   bf16* Qs = reinterpret_cast<bf16*>(lm_raw);          // [QB][16][LDQ]
-  bf16* Ct = Qs + (size_t)LM_QB * 16 * LDQ;            // [TJ][LDQ]
+  bf16* Ct0 = Qs + (size_t)LM_QB * 16 * LDQ;           // two tiles [TJ][LDQ]: one is read while the next one arrives (cp.async)
   const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wq = warp / RS, wr = warp - wq * RS;
-  const int m0 = blockIdx.x * LM_QB, h0 = blockIdx.y * 16, z = blockIdx.z;
+  // the last queries see the most keys: their blocks start first
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * LM_QB, h0 = blockIdx.y * 16, z = blockIdx.z;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
   const int nk_max = P + min(o.M, m0 + LM_QB);
   int per = (nk_max + splits - 1) / splits;
@@ -735,10 +784,10 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   const bool active = m < o.M;
   const int nk = min(P + m + 1, j1);                   // this query's keys end here (inside this split)
   const float* A = reinterpret_cast<const float*>(o.A);
-  for (int i = tid; i < LM_QB * 16 * R; i += nth) {
+  const int nq = min(LM_QB, o.M - m0);                 // live queries of this block: the others' warps never read their rows
+  for (int i = tid; i < nq * 16 * R; i += nth) {
     const int q = i / (16 * R), rem = i - q * 16 * R, h = rem / R, r = rem - h * R;
-    const int mm = m0 + q;
-    const float v = (mm < o.M && h0 + h < H) ? A[(size_t)mm * o.lda + (size_t)(h0 + h) * R + r] * o.f0 : 0.f;
+    const float v = h0 + h < H ? A[(size_t)(m0 + q) * o.lda + (size_t)(h0 + h) * R + r] * o.f0 : 0.f;
     Qs[(q * 16 + h) * LDQ + r] = __float2bfloat16_rn(v);
   }
   float oacc[NTM][4];
@@ -749,30 +798,46 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   const bf16* cache = reinterpret_cast<const bf16*>(o.B);
   const int chunks = R >> 3;
   const bf16* Qw = Qs + (size_t)wq * 16 * LDQ;
-  __syncthreads();
-  for (int jt = j0; jt < j1; jt += TJ) {
+  auto fetch_tile = [&](const int jt, bf16* dst) {       // rows beyond the range arrive as zeros
     for (int i = tid; i < TJ * chunks; i += nth) {
       const int row = i / chunks, c = i - row * chunks;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (jt + row < j1) v = *reinterpret_cast<const uint4*>(cache + (size_t)(jt + row) * o.ldr + c * 8);
-      *reinterpret_cast<uint4*>(Ct + (size_t)row * LDQ + c * 8) = v;
+      const bool ok = jt + row < j1;
+      cp_async16(dst + (size_t)row * LDQ + c * 8, cache + (size_t)(ok ? jt + row : j0) * o.ldr + c * 8, ok);
+    }
+    cp_async_commit();
+  };
+  if (j0 < j1) fetch_tile(j0, Ct0);
+  int it = 0;
+  for (int jt = j0; jt < j1; jt += TJ, ++it) {
+    bf16* Ct = Ct0 + (size_t)(it & 1) * TJ * LDQ;
+    if (jt + TJ < j1) {
+      fetch_tile(jt + TJ, Ct0 + (size_t)((it + 1) & 1) * TJ * LDQ);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
     if (active && jt < nk) {
       float s[8][4];
 #pragma unroll
       for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
-      for (int kk = 0; kk < R; kk += 16) {
-        uint32_t a[4];
-        a[0] = *reinterpret_cast<const uint32_t*>(Qw + g * LDQ + kk + t * 2);
-        a[1] = *reinterpret_cast<const uint32_t*>(Qw + (g + 8) * LDQ + kk + t * 2);
-        a[2] = *reinterpret_cast<const uint32_t*>(Qw + g * LDQ + kk + 8 + t * 2);
-        a[3] = *reinterpret_cast<const uint32_t*>(Qw + (g + 8) * LDQ + kk + 8 + t * 2);
+      {
+        const int mi = lane >> 3, l7 = lane & 7;
+        // ldmatrix lanes: A = 16 heads x 16 columns of the query (matrices: rows 0-7 / 8-15 at kk, then at kk + 8);
+        // B = two key octets x 16 columns of the tile (matrices: octet nt at kk, kk + 8, octet nt + 1 at kk, kk + 8)
+        const bf16* qa = Qw + (size_t)((mi & 1) * 8 + l7) * LDQ + (mi >> 1) * 8;
+        const bf16* cb = Ct + (size_t)((mi >> 1) * 8 + l7) * LDQ + (mi & 1) * 8;
+        for (int kk = 0; kk < R; kk += 16) {
+          uint32_t a[4];
+          ldmatrix_x4(a, qa + kk);
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          if (nt * 8 < TJ) {
-            const bf16* bp = Ct + (size_t)(nt * 8 + g) * LDQ + kk + t * 2;
-            mma16816(s[nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+          for (int nt = 0; nt < 8; nt += 2) {
+            if (nt * 8 < TJ) {
+              uint32_t b[4];
+              ldmatrix_x4(b, cb + (size_t)nt * 8 * LDQ + kk);
+              mma16816(s[nt], a, b[0], b[1]);
+              mma16816(s[nt + 1], a, b[2], b[3]);
+            }
           }
         }
       }
@@ -823,12 +888,11 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
             if (nt < nt_o) {
               uint32_t b[4];
               ldmatrix_x4_trans(b, base + nt * 8);
+              const bool two = nt + 1 < nt_o;       // high parts first: consecutive MMAs do not wait on one accumulator
               mma16816(oacc[nt], ah, b[0], b[1]);
+              if (two) mma16816(oacc[nt + 1], ah, b[2], b[3]);
               mma16816(oacc[nt], al, b[0], b[1]);
-              if (nt + 1 < nt_o) {
-                mma16816(oacc[nt + 1], ah, b[2], b[3]);
-                mma16816(oacc[nt + 1], al, b[2], b[3]);
-              }
+              if (two) mma16816(oacc[nt + 1], al, b[2], b[3]);
             }
           }
         }

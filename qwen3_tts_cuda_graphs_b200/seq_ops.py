@@ -138,7 +138,9 @@ class StepBuilder:
         ctab = self.slot.cur[cache]
         self.group_norm(qd, w["dkv_norm"], 1, eps, ctab, n=R, col=H * c.dim, append_at_position=True)
         qa = self.block_linear(qd, w["uk_t"], self.buf("la.qa", M, H * R))
-        splits = 1 if M >= 64 else (4 if M > 8 else 16)
+        # key-range splits: a long step has blocks enough; a few rows (decoding) spread their keys over up to 64 blocks of one or
+        # more 64-key tiles each, sized by what the slot can hold (the list is built once for every position)
+        splits = 1 if M >= 64 else (4 if M > 8 else max(1, min(64, -(-self.slot.max_pos // 64))))
         oa = self.buf("la.oa", M, H * R)
         kw = dict(M=M, N=H * R, K=splits, i0=H, i1=R, i2=H, f0=c.scale, A=qa, lda=qa.shape[1], B=ctab, ldr=ctab.shape[1], p0=self.slot.pos,
                   C=oa, ldc=oa.shape[1], flags=F_F32 if ctab.dtype == torch.float32 else 0)
