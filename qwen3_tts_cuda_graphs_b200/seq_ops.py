@@ -140,7 +140,10 @@ class StepBuilder:
         qa = self.block_linear(qd, w["uk_t"], self.buf("la.qa", M, H * R))
         # key-range splits: a long step has blocks enough; a few rows (decoding) spread their keys over up to 64 blocks of one or
         # more 64-key tiles each, sized by what the slot can hold (the list is built once for every position)
-        splits = 1 if M >= 64 else (4 if M > 8 else max(1, min(64, -(-self.slot.max_pos // 64))))
+        # (the tensor-core kernel runs 4 queries x 16 heads per block, the CUDA-core one a query per block; ~2 blocks per SM wanted)
+        tiles = max(1, -(-self.slot.max_pos // 64))
+        blocks = M if ctab.dtype == torch.float32 else -(-M // 4) * -(-H // 16)
+        splits = min(64, tiles) if M <= 8 else max(1, min(16, tiles, -(-296 // blocks)))
         oa = self.buf("la.oa", M, H * R)
         kw = dict(M=M, N=H * R, K=splits, i0=H, i1=R, i2=H, f0=c.scale, A=qa, lda=qa.shape[1], B=ctab, ldr=ctab.shape[1], p0=self.slot.pos,
                   C=oa, ldc=oa.shape[1], flags=F_F32 if ctab.dtype == torch.float32 else 0)
