@@ -58,6 +58,17 @@ def aligned():
     ])
 
 
+def mid():
+    """Sizes at which every product takes its real-size kernel (128-row tensor-core tiles, the attention's 16-head blocks with
+    a second, part-filled block, two accumulator widths, grouped expert tiles), still quick for the float64 oracle."""
+    return config(1000, 256, 4, 3, [
+        layer(attn(20, 32, 48, 144, 0.2), moe(12, 4, 3, 4, 2, 2.0, 128, 256)),
+        layer(lru(384, 6, 4), dense(512)),
+        layer(attn(4, 64, 32, 256, 0.15), moe(8, 0, 2, 1, 1, 1.0, 192, 0)),
+        layer(lru(128, 2, 2), None),
+    ])
+
+
 def weights(cfg, seed=0, peaky=0.0, sink=None, optional=True):
     """Random weights rounded to bf16 (so that bf16 and f32 runs hold the same numbers).  peaky > 0 multiplies the query
     projections: softmax rows collapse onto single keys, so a key that is one position off changes the output visibly.

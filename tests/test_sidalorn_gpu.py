@@ -294,6 +294,19 @@ def test_prompt_portions_and_decoding_agree_with_the_oracle(case, f32):
     eng.close_all()
 
 
+@pytest.mark.parametrize("f32", [True, False])
+def test_real_size_kernel_paths_agree_with_the_oracle(f32):
+    """A prompt long enough for full 128-row product tiles and several key tiles, in one step and in portions, then decoding."""
+    cfg = cases.mid()
+    W = cases.weights(cfg, seed=11)
+    toks = cases.tokens(cfg, 300)
+    want = so.forward(cfg, W, toks)
+    eng = make_engine(cfg, W, f32)
+    for portions in ([300], [130, 2, 140], [257, 9, 31]):
+        assert close_enough(run_schedule(eng, toks, portions), want, f32), portions
+    eng.close_all()
+
+
 def test_optional_tensors_may_be_absent():
     cfg = cases.odd()
     W = cases.weights(cfg, seed=8, optional=False)
