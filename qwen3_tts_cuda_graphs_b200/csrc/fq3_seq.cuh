@@ -261,6 +261,100 @@ __global__ void __launch_bounds__(128) fq3s_gemm_mma_kernel(const SeqGemm g) {
       }
 }
 
+// The same product for tall operands (hundreds of rows per block / expert): 128 x 128 x 32 tiles, eight warps of 64 x 32 each, fragments
+// by ldmatrix.  Halves the operand traffic per output of the 64 x 64 kernel and runs 16 MMAs per warp between two barriers.
+template <typename TA>
+__global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) {
+  constexpr int LD = 32 + 8, BM = 128, BN = 128;
+  __shared__ __align__(16) bf16 As[BM * LD];
+  __shared__ __align__(16) bf16 Bs[BN * LD];
+  const int tid = threadIdx.x, z = blockIdx.z, warp = tid >> 5, lane = tid & 31;
+  int row0, row_end;
+  const bf16* Bp = reinterpret_cast<const bf16*>(g.B) + (size_t)z * g.b_zstride;
+  if (g.seg) {
+    int t = blockIdx.y, e = 0;
+    row0 = -1; row_end = 0;
+    for (; e < g.E; ++e) {
+      const int s0 = g.seg[e], s1 = g.seg[e + 1];
+      const int nt = (s1 - s0 + BM - 1) / BM;
+      if (t < nt) { row0 = s0 + t * BM; row_end = s1; break; }
+      t -= nt;
+    }
+    if (row0 < 0) return;
+    Bp += (size_t)e * g.b_estride;
+  } else {
+    row0 = blockIdx.y * BM; row_end = g.M;
+  }
+  const int col0 = blockIdx.x * BN;
+  const TA* Ap = reinterpret_cast<const TA*>(g.A) + (size_t)(z % g.a_mod) * g.a_zstride;
+  const int lr = tid >> 1, lk = (tid & 1) * 16;       // loaders: thread -> (row = tid / 2, 16 consecutive k)
+  const int ar = row0 + lr;
+  const TA* a_ptr = nullptr;
+  if (ar < row_end) a_ptr = Ap + (size_t)(g.rows ? g.rows[ar] : ar) * g.lda + lk;
+  const int bn = col0 + lr;
+  const bf16* b_ptr = bn < g.N ? Bp + (size_t)bn * g.ldb + lk : nullptr;
+  constexpr int AV = 16 / sizeof(TA);
+  const bool vec_a = (g.lda % AV == 0) && ((reinterpret_cast<uintptr_t>(Ap) & 15) == 0);
+  const bool vec_b = (g.ldb % 8 == 0) && ((reinterpret_cast<uintptr_t>(Bp) & 15) == 0);
+  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  // ldmatrix lanes.  A (row-major [m][k]): matrices rows 0-7 / 8-15 at k, then at k + 8.  B ([n][k]): columns n 0-7 at k, k + 8, then n 8-15.
+  const bf16* a_lane = As + (size_t)(wm + (lane & 15)) * LD + (lane >> 4) * 8;
+  const bf16* b_lane = Bs + (size_t)(wn + (lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8;
+  uint4 ra[2], rb[2];
+  sg_fetch16<TA>(a_ptr, vec_a, g.K - lk, ra);
+  sg_fetch16<bf16>(b_ptr, vec_b, g.K - lk, rb);
+  for (int k0 = 0; k0 < g.K; k0 += 32) {
+    *reinterpret_cast<uint4*>(&As[lr * LD + lk]) = ra[0];
+    *reinterpret_cast<uint4*>(&As[lr * LD + lk + 8]) = ra[1];
+    *reinterpret_cast<uint4*>(&Bs[lr * LD + lk]) = rb[0];
+    *reinterpret_cast<uint4*>(&Bs[lr * LD + lk + 8]) = rb[1];
+    __syncthreads();
+    if (k0 + 32 < g.K) {
+      sg_fetch16<TA>(a_ptr ? a_ptr + k0 + 32 : nullptr, vec_a, g.K - (k0 + 32 + lk), ra);
+      sg_fetch16<bf16>(b_ptr ? b_ptr + k0 + 32 : nullptr, vec_b, g.K - (k0 + 32 + lk), rb);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 32; kk += 16) {
+      uint32_t a[4][4], b[2][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ldmatrix_x4(a[i], a_lane + (size_t)i * 16 * LD + kk);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) ldmatrix_x4(b[j], b_lane + (size_t)j * 16 * LD + kk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma16816(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+  const int ccol = z * g.c_zstride;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = row0 + wm + i * 16 + (lane >> 2) + (q >> 1) * 8;
+        const int n = col0 + wn + j * 8 + (lane & 3) * 2 + (q & 1);
+        if (r >= row_end || n >= g.N) continue;
+        float v = acc[i][j][q];
+        if (g.flags & FQ3C_BIAS) v += g.bias[ccol + n];
+        if (g.flags & FQ3C_GELU) v = gelu_f(v);
+        if (g.flags & FQ3C_GELU_TANH) v = gelu_tanh_f(v);
+        if (g.flags & FQ3C_SIGMOID) v = sigmoid_f(v);
+        const size_t ci = (size_t)r * g.ldc + ccol + n;
+        if (g.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(g.C)[ci] = v;
+        else reinterpret_cast<bf16*>(g.C)[ci] = __float2bfloat16_rn(v);
+      }
+}
+
 // One output row with few rows in flight (decode: M <= 8): a warp per output column streams its weight row once, 16 bytes per
 // lane and load, and dots it with every A row (f32 or bf16 in shared memory as f32).  Weight-streaming bound.
 template <typename TA, typename TB>

@@ -270,6 +270,36 @@ def test_moe_ff_alone(experts, identity, top, count, keep, shared):
     assert float((out.cpu().to(F64) - want).abs().max() / want.abs().max()) < 2e-5
 
 
+def test_moe_ff_many_tokens_per_expert_bf16():
+    """Hundreds of rows per expert in bf16: the grouped products take their tall tensor-core tiles, with gathered rows, segments
+    that end inside a tile, an expert nobody chooses (its correction is very negative) and identity choices that leave no row."""
+    from qwen3_tts_cuda_graphs_b200.config import MoEFFConfig
+
+    g = torch.Generator().manual_seed(12)
+    experts, identity, top, width, ff, T = 4, 1, 2, 136, 152, 700
+    n = experts + identity
+    r = lambda *sh, k=1.0: (k * torch.randn(*sh, generator=g)).to(torch.bfloat16).float()
+    W = {"router": r(n, width, k=width ** -0.5), "correction": torch.tensor([0.0, -50.0, 0.1, 0.0, 0.05])}
+    for e in range(experts):
+        W[f"e{e}.up"] = r(ff, width, k=width ** -0.5)
+        W[f"e{e}.down"] = r(width, ff, k=ff ** -0.5)
+    h = r(T, width)
+    f = {"router": {"experts": experts, "identity": identity, "top": top, "scale": 1.3, "groups": {"count": 1, "keep": 1}}, "shared": None}
+    W64 = {"m." + k: v.to(F64) for k, v in W.items()}
+    want = so.moe_ff(h.to(F64), W64, "m.", f)
+    ids, _ = so.route(h.to(F64), W64, "m.", f["router"])
+    assert not bool((ids == 1).any()) and bool((ids == 4).any()) and int((ids == 0).sum()) > 128
+    bf = torch.bfloat16
+    pw = {"router": cuda(W["router"], bf), "correction": cuda(W["correction"]),
+          "up": cuda(torch.stack([W[f"e{e}.up"] for e in range(experts)]), bf), "down": cuda(torch.stack([W[f"e{e}.down"] for e in range(experts)]), bf),
+          "shared_up": None, "shared_down": None}
+    out = torch.zeros(T, width, device="cuda")
+    bench = Bench([], f32=False, max_pos=T)
+    bench.run(T, lambda b: b.moe_ff(cuda(h), cuda(h, bf), MoEFFConfig(experts, identity, top, 1, 1, 1.3, ff, 0), pw, out))
+    err = (out.cpu().to(F64) - want).abs().amax(-1) / want.abs().max()
+    assert float(err.quantile(0.98)) < 2e-2 and float(err.median()) < 5e-3, (float(err.max()), float(err.median()))
+
+
 # ---------------------------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------------------------
