@@ -977,16 +977,25 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
           }
           const int mi = lane >> 3;
           const bf16* base = Ct + (size_t)(ks * 16 + (mi & 1) * 8 + (lane & 7)) * LDQ + c0 + (mi >> 1) * 8;
+          // eight column octets at a time: their high-part MMAs, then their low-part ones, so that an accumulator's two MMAs
+          // are eight apart and none waits for the one before it
 #pragma unroll
-          for (int nt = 0; nt < NTM; nt += 2) {
-            if (nt < nt_o) {
-              uint32_t b[4];
-              ldmatrix_x4_trans(b, base + nt * 8);
-              const bool two = nt + 1 < nt_o;       // high parts first: consecutive MMAs do not wait on one accumulator
-              mma16816(oacc[nt], ah, b[0], b[1]);
-              if (two) mma16816(oacc[nt + 1], ah, b[2], b[3]);
-              mma16816(oacc[nt], al, b[0], b[1]);
-              if (two) mma16816(oacc[nt + 1], al, b[2], b[3]);
+          for (int nt0 = 0; nt0 < NTM; nt0 += 8) {
+            uint32_t b[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (nt0 + 2 * q < nt_o) ldmatrix_x4_trans(b[q], base + (nt0 + 2 * q) * 8);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int nt = nt0 + 2 * q;
+              if (nt < nt_o) mma16816(oacc[nt], ah, b[q][0], b[q][1]);
+              if (nt + 1 < nt_o) mma16816(oacc[nt + 1], ah, b[q][2], b[q][3]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int nt = nt0 + 2 * q;
+              if (nt < nt_o) mma16816(oacc[nt], al, b[q][0], b[q][1]);
+              if (nt + 1 < nt_o) mma16816(oacc[nt + 1], al, b[q][2], b[q][3]);
             }
           }
         }
