@@ -143,7 +143,7 @@ class StepBuilder:
         # (the tensor-core kernel runs 4 queries x 16 heads per block, the CUDA-core one a query per block; ~2 blocks per SM wanted)
         tiles = max(1, -(-self.slot.max_pos // 64))
         blocks = M if ctab.dtype == torch.float32 else -(-M // 4) * -(-H // 16)
-        splits = min(64, tiles) if M <= 8 else max(1, min(16, tiles, -(-296 // blocks)))
+        splits = min(64, tiles) if M <= 8 else (1 if blocks >= 74 else max(1, min(16, tiles, -(-296 // blocks))))   # half the SMs busy: no split
         oa = self.buf("la.oa", M, H * R)
         kw = dict(M=M, N=H * R, K=splits, i0=H, i1=R, i2=H, f0=c.scale, A=qa, lda=qa.shape[1], B=ctab, ldr=ctab.shape[1], p0=self.slot.pos,
                   C=oa, ldc=oa.shape[1], flags=F_F32 if ctab.dtype == torch.float32 else 0)
