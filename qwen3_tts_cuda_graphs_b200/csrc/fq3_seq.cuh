@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) fq3s_gemm_kernel(const SeqGemm g) {
   }
 }
 
-// Same contract on the bf16 tensor cores (mma.sync m16n8k16, f32 accumulate) for bf16 weights: the block-diagonal and grouped
+// Same interface on the bf16 tensor cores (mma.sync m16n8k16, f32 accumulate) for bf16 weights: the block-diagonal and grouped
 // products of real-size layers.  64 x 64 x 32 tiles, four warps, each a 32 x 32 quadrant.  A may be f32 (rounded to bf16 as it is
 // staged, which is what a bf16 product does to its operand) and rows may be gathered.  Every thread stages 16 consecutive k of
 // one A row and one B row: with 16-byte loads where the operand's rows allow it (`vec`), element by element otherwise and at

@@ -42,12 +42,12 @@ def sizes():
     def model(width, heads, rank, lru_blocks, dense_ff, experts, top, expert_ff, shared_ff, vocab=3072, pairs=2):
         att = LatentAttentionConfig(heads, 128, 128, rank, 128 ** -0.5)
         lru = RglruConfig(width, lru_blocks, 4)
-        moe = MoEFFConfig(experts, 2, top, 2, 1, 2.5, expert_ff, shared_ff)
+        moe = MoEFFConfig(experts, 2, top, 4, 2, 2.0, expert_ff, shared_ff)
         layers = []
         for _ in range(pairs):
             layers += [SeqLayerConfig("rglru", lru, DenseFFConfig(dense_ff)), SeqLayerConfig("latent_attention", att, moe),
                        SeqLayerConfig("latent_attention", att, moe)]
-        return SidalornConfig(vocab, width, 1e-6, 2, 4, tuple(layers))
+        return SidalornConfig(vocab, width, 1e-5, 4, 3, tuple(layers))
 
     return {"w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1)}
 

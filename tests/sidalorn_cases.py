@@ -38,7 +38,7 @@ def odd():
         layer(attn(2, 8, 8, 12, 0.5), None),
         layer(lru(40, 1, 1), moe(4, 0, 1, 1, 1, 1.0, 16, 0)),
         layer(attn(5, 16, 8, 36, 0.25), moe(5, 3, 2, 2, 1, 2.5, 32, 40)),
-    ])
+    ], eps=1e-2)      # large enough to change every norm visibly: a norm that ignores the configured value fails
 
 
 def unaligned():
@@ -66,7 +66,7 @@ def mid():
         layer(lru(384, 6, 4), dense(512)),
         layer(attn(4, 64, 32, 256, 0.15), moe(8, 0, 2, 1, 1, 1.0, 192, 0)),
         layer(lru(128, 2, 2), None),
-    ])
+    ], eps=1e-5)
 
 
 def weights(cfg, seed=0, peaky=0.0, sink=None, optional=True):
