@@ -137,3 +137,26 @@ def weights(cfg, seed=0, peaky=0.0, sink=None, optional=True):
 def tokens(cfg, n, seed=0):
     g = torch.Generator().manual_seed(1000 + seed)
     return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
+
+
+def save_checkpoint(folder, cfg, W):
+    """config.json and model.safetensors (bf16) in `folder`: 8-byte little-endian header length, JSON header, tensor bytes."""
+    import json
+    import os
+    import struct
+
+    header, blobs, at = {}, [], 0
+    for name, t in W.items():
+        raw = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for raw in blobs:
+            f.write(raw)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)

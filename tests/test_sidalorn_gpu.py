@@ -468,3 +468,40 @@ def test_greedy_generation_through_engine_and_scheduler():
     sched.run()
     assert h.result()[:min(4, len(want[0]))] == want[0][:4]
     eng.close_all()
+
+
+def test_replayer_reads_a_checkpoint_from_disk_and_writes_the_wanted_logits(tmp_path):
+    """bin/trace_run as a child process: config.json + model.safetensors on disk, steps on standard input (a portion with
+    several wanted places, a two-token portion with none, single tokens, a finished request whose slot the next one takes),
+    one file of little-endian f32 logits per step that wants some, "done <step>" after every step."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    cfg = cases.odd()
+    W = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in cases.weights(cfg, seed=21).items()}   # what the file holds
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    model_dir.mkdir()
+    cases.save_checkpoint(str(model_dir), cfg, W)
+    a, b = cases.tokens(cfg, 14, seed=5), cases.tokens(cfg, 6, seed=6)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:9], "want": [0, 3, 8]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[9:11], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[11:12], "want": [0]}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[12:14], "want": [1, 0]}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "b", "tokens": b, "want": [5]}], "end": ["b"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", "float32",
+                        "--out", str(out_dir), "--max-tokens", "16", "--max-slots", "1"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.splitlines() if ln.startswith("done ")] == [f"done {i}" for i in range(5)]
+    assert not (out_dir / "1.f32").exists()
+    ref_a, ref_b = so.forward(cfg, W, a), so.forward(cfg, W, b)
+    for step, ref, places in ((0, ref_a, [0, 3, 8]), (2, ref_a, [11]), (3, ref_a, [13, 12]), (4, ref_b, [5])):
+        got = torch.from_numpy(np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(places), cfg["vocab"]))
+        assert rel_err(got, ref[places]) < TOL[True], step
