@@ -1122,6 +1122,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
     case FQ3C_LATENT_ATTN: {
       if (o.i0 < 1 || o.i1 < 1 || !o.A || !o.B || !o.C) return fail("latent_attn: missing operand");
       const int splits = std::max(1, o.K);
+      if (splits > 64) return fail("latent_attn: at most 64 key splits");
       if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.i1 + 2) * 4)) return fail("latent_attn: workspace too small for the splits");
       // bf16 cache with a rank the MMA tiles divide: the tensor-core kernel (FQ3S_ATTN_MMA=0: CUDA cores everywhere)
       static int use_mma = -1;
@@ -1130,8 +1131,14 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       if (use_mma && !(o.flags & FQ3C_F32) && RS <= 2 && o.i1 % 16 == 0 && o.i1 % (8 * RS) == 0 && o.ldr % 8 == 0 &&
           !(reinterpret_cast<uintptr_t>(o.B) & 15)) {
         const int TJ = o.i1 > 256 ? 32 : 64;
-        const size_t smem = (size_t)(LM_QB * 16 + 2 * TJ) * (o.i1 + 8) * 2;   // queries + two key tiles
-        const int nt_o = (o.i1 / RS) / 8;
+        // one query (decoding): a block per split with all its warps on that query, R cut into up to eight 16-column-aligned slices
+        int QB = LM_QB, RSk = RS;
+        if (o.M == 1) {
+          QB = 1;
+          while (RSk < 8 && o.i1 % (32 * RSk) == 0) RSk *= 2;
+        }
+        const size_t smem = (size_t)(QB * 16 + 2 * TJ) * (o.i1 + 8) * 2;   // queries + two key tiles
+        const int nt_o = (o.i1 / RSk) / 8;
         static bool mattr[64] = {};
         int dev = 0;
         cudaGetDevice(&dev);
@@ -1141,11 +1148,11 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
           cudaFuncSetAttribute(fq3s_latent_attn_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
           mattr[dev] = true;
         }
-        dim3 grid((o.M + LM_QB - 1) / LM_QB, (o.i0 + 15) / 16, splits);
-        const int nth = 32 * LM_QB * RS;
-        if (nt_o <= 8) fq3s_latent_attn_mma_kernel<8><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
-        else if (nt_o <= 16) fq3s_latent_attn_mma_kernel<16><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
-        else fq3s_latent_attn_mma_kernel<32><<<grid, nth, smem, s>>>(o, RS, splits, TJ);
+        dim3 grid((o.M + QB - 1) / QB, (o.i0 + 15) / 16, splits);
+        const int nth = 32 * QB * RSk;
+        if (nt_o <= 8) fq3s_latent_attn_mma_kernel<8><<<grid, nth, smem, s>>>(o, RSk, splits, TJ, QB);
+        else if (nt_o <= 16) fq3s_latent_attn_mma_kernel<16><<<grid, nth, smem, s>>>(o, RSk, splits, TJ, QB);
+        else fq3s_latent_attn_mma_kernel<32><<<grid, nth, smem, s>>>(o, RSk, splits, TJ, QB);
         if (splits > 1) {
           fq3s_latent_merge_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o, splits);
           count_launches(1);

@@ -363,37 +363,60 @@ __global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
   const int z = blockIdx.z;
   const TA* Ap = reinterpret_cast<const TA*>(g.A) + (size_t)(z % g.a_mod) * g.a_zstride;
   const TB* Bp = reinterpret_cast<const TB*>(g.B) + (size_t)z * g.b_zstride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  const TB* w = Bp + (size_t)min(n, g.N - 1) * g.ldb;
+  constexpr int VEC = 16 / sizeof(TB);
+  constexpr int U = 4;                 // 16-byte weight loads a lane keeps in flight
+  const bool vec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (g.K % VEC == 0);
+  // the first weight loads leave before the rows are staged: the two latencies overlap
+  uint4 raw[U];
+  if (vec && n < g.N) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (lane + 32 * u) * VEC;
+      raw[u] = k < g.K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   for (int i = threadIdx.x; i < g.M * g.K; i += blockDim.x) {
     const int m = i / g.K, k = i - m * g.K;
     xs[i] = ldf<TA>(Ap + (size_t)m * g.lda + k);
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 8 + warp;
   if (n >= g.N) return;
-  const TB* w = Bp + (size_t)n * g.ldb;
   float acc[8];
 #pragma unroll
   for (int m = 0; m < 8; ++m) acc[m] = 0.f;
-  constexpr int VEC = 16 / sizeof(TB);
-  const bool vec = ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (g.K % VEC == 0);
   if (vec) {
-    for (int k = lane * VEC; k < g.K; k += 32 * VEC) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
-      float wv[VEC];
-      if (sizeof(TB) == 2) {
-        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+    for (int k0 = lane * VEC; k0 < g.K; k0 += 32 * U * VEC) {
+      uint4 nxt[U];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) { wv[(2 * q) % VEC] = __uint_as_float(u[q] << 16); wv[(2 * q + 1) % VEC] = __uint_as_float(u[q] & 0xffff0000u); }
-      } else {
-        wv[0] = __uint_as_float(raw.x); wv[1] = __uint_as_float(raw.y); wv[2 % VEC] = __uint_as_float(raw.z); wv[3 % VEC] = __uint_as_float(raw.w);
+      for (int u = 0; u < U; ++u) {      // the next batch is on its way while this one is used
+        const int k = k0 + 32 * (U + u) * VEC;
+        nxt[u] = k < g.K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
-      for (int m = 0; m < 8; ++m)
-        if (m < g.M) {
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + 32 * u * VEC;
+        if (k < g.K) {
+          float wv[VEC];
+          if (sizeof(TB) == 2) {
+            const uint32_t q4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-          for (int q = 0; q < VEC; ++q) acc[m] = fmaf(wv[q], xs[m * g.K + k + q], acc[m]);
+            for (int q = 0; q < 4; ++q) { wv[(2 * q) % VEC] = __uint_as_float(q4[q] << 16); wv[(2 * q + 1) % VEC] = __uint_as_float(q4[q] & 0xffff0000u); }
+          } else {
+            wv[0] = __uint_as_float(raw[u].x); wv[1] = __uint_as_float(raw[u].y); wv[2 % VEC] = __uint_as_float(raw[u].z); wv[3 % VEC] = __uint_as_float(raw[u].w);
+          }
+#pragma unroll
+          for (int m = 0; m < 8; ++m)
+            if (m < g.M) {
+#pragma unroll
+              for (int q = 0; q < VEC; ++q) acc[m] = fmaf(wv[q], xs[m * g.K + k + q], acc[m]);
+            }
         }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) raw[u] = nxt[u];
     }
   } else {
     for (int k = lane; k < g.K; k += 32) {
@@ -818,25 +841,44 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_kernel(const fq3c_op o, 
     }
   }
 }
-// grid (M, H)
+// grid (M, H).  The splits' maxima and sums are read once (a thread per split), their weights exp(max_s - max) live in shared
+// memory, and every thread then adds its columns with the loads of eight splits in flight.
 __global__ void __launch_bounds__(128) fq3s_latent_merge_kernel(const fq3c_op o, const int splits) {
+  __shared__ float wsm[64];
+  __shared__ float red[8];
   const int R = o.i1, H = o.i0, m = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* base = reinterpret_cast<const float*>(o.ws) + ((size_t)m * H + h) * splits * (R + 2);
   const float* sink = reinterpret_cast<const float*>(o.scale);
-  float mm = sink ? sink[h] : -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[(size_t)s * (R + 2)]);
-  float den = sink ? expf(sink[h] - mm) : 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = base[(size_t)s * (R + 2)];
-    if (ms != -INFINITY) den += base[(size_t)s * (R + 2) + 1] * expf(ms - mm);
-  }
+  const float sk = sink ? sink[h] : -INFINITY;
+  const float ms = tid < splits ? base[(size_t)tid * (R + 2)] : -INFINITY;
+  const float ls = tid < splits ? base[(size_t)tid * (R + 2) + 1] : 0.f;
+  float mm = fmaxf(ms, sk);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, d));
+  if (lane == 0) red[warp] = mm;
+  __syncthreads();
+  mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  const float wt = ms == -INFINITY ? 0.f : expf(ms - mm);
+  if (tid < splits) wsm[tid] = wt;
+  float den = ls * wt;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) den += __shfl_xor_sync(0xffffffffu, den, d);
+  if (lane == 0) red[4 + warp] = den;
+  __syncthreads();
+  den = red[4] + red[5] + red[6] + red[7] + (sink ? expf(sk - mm) : 0.f);
   float* c = reinterpret_cast<float*>(o.C) + (size_t)m * o.ldc + (size_t)h * R;
-  for (int r = threadIdx.x; r < R; r += blockDim.x) {
+  for (int r = tid; r < R; r += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = base[(size_t)s * (R + 2)];
-      if (ms != -INFINITY) acc = fmaf(base[(size_t)s * (R + 2) + 2 + r], expf(ms - mm), acc);
+    int s = 0;
+    for (; s + 8 <= splits; s += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = base[(size_t)(s + u) * (R + 2) + 2 + r];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = fmaf(v[u], wsm[s + u], acc);
     }
+    for (; s < splits; ++s) acc = fmaf(base[(size_t)s * (R + 2) + 2 + r], wsm[s], acc);
     c[r] = acc / den;
   }
 }
@@ -846,7 +888,8 @@ __global__ void __launch_bounds__(128) fq3s_latent_merge_kernel(const fq3c_op o,
 // latent row, so scores S [16 heads x TJ keys] = Q' [16 x R] . C^T and outputs O' [16 x R] += P [16 x TJ] . C [TJ x R] are
 // m16n8k16 tiles whose B operand is the staged tile of latent rows itself (row-major for the scores, ldmatrix.trans for the
 // outputs).  A block takes QB = 4 consecutive queries (they see almost the same keys) x RS slices of R (<= 256 columns of O' per
-// warp: 128 accumulator registers); the RS warps of a query compute its scores redundantly.  Scores, maxima, sums and the
+// warp: 128 accumulator registers); the RS warps of a query compute its scores redundantly.  A single query (decoding) gets a
+// block of its own (QB = 1) whose up to eight warps split R.  Scores, maxima, sums and the
 // rescaling are f32; a weight enters the output product as a bf16 pair p_hi + p_lo (two MMAs), i.e. with 16 mantissa bits, the
 // query as one bf16 (the rounding a bf16 product applies to its operand).  grid (ceil(M / 4), ceil(H / 16), splits).
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -860,17 +903,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 template <int NTM>
-__global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op o, const int RS, const int splits, const int TJ) {
+__global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op o, const int RS, const int splits, const int TJ, const int QB) {
   extern __shared__ __align__(16) unsigned char lm_raw[];
   const int R = o.i1, H = o.i0, LDQ = R + 8;
   bf16* Qs = reinterpret_cast<bf16*>(lm_raw);          // [QB][16][LDQ]
-  bf16* Ct0 = Qs + (size_t)LM_QB * 16 * LDQ;           // two tiles [TJ][LDQ]: one is read while the next one arrives (cp.async)
+  bf16* Ct0 = Qs + (size_t)QB * 16 * LDQ;           // two tiles [TJ][LDQ]: one is read while the next one arrives (cp.async)
   const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int wq = warp / RS, wr = warp - wq * RS;
   // the last queries see the most keys: their blocks start first
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * LM_QB, h0 = blockIdx.y * 16, z = blockIdx.z;
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * QB, h0 = blockIdx.y * 16, z = blockIdx.z;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
-  const int nk_max = P + min(o.M, m0 + LM_QB);
+  const int nk_max = P + min(o.M, m0 + QB);
   int per = (nk_max + splits - 1) / splits;
   per = (per + TJ - 1) / TJ * TJ;
   const int j0 = z * per, j1 = min(nk_max, j0 + per);
@@ -878,7 +921,7 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
   const bool active = m < o.M;
   const int nk = min(P + m + 1, j1);                   // this query's keys end here (inside this split)
   const float* A = reinterpret_cast<const float*>(o.A);
-  const int nq = min(LM_QB, o.M - m0);                 // live queries of this block: the others' warps never read their rows
+  const int nq = min(QB, o.M - m0);                 // live queries of this block: the others' warps never read their rows
   for (int i = tid; i < nq * 16 * R; i += nth) {
     const int q = i / (16 * R), rem = i - q * 16 * R, h = rem / R, r = rem - h * R;
     const float v = h0 + h < H ? A[(size_t)(m0 + q) * o.lda + (size_t)(h0 + h) * R + r] * o.f0 : 0.f;
