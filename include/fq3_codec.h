@@ -74,7 +74,9 @@ enum fq3c_kind {
   FQ3C_ROUTER = 19,   /* mixture-of-experts router: A = f32 logits [M, N]; s = softmax over N; choice = s + bias (f32 [N], may be
                          NULL); experts form i1 equal groups of neighbours, a group's score is its largest choice, only the best i2
                          groups stay eligible; the i0 largest eligible choices are taken (lower index wins a tie);
-                         weights = s[chosen] / (sum + 1e-20) * f0.  C = int32 [M, i0] expert ids, C2 = f32 [M, i0] weights        */
+                         weights = s[chosen] / (sum + 1e-20) * f0.  C = int32 [M, i0] expert ids, C2 = f32 [M, i0] weights.
+                         With ws set (M = 1, i0 <= 16) the launch also does FQ3C_MOE_SORT's grouping: K = experts that are real,
+                         p0 = segment starts, p1 = token of each sorted position, ws = sorted position of each choice or -1     */
   FQ3C_MOE_SORT = 20, /* A = int32 ids [M, i0]; experts with id < i1 are real.  C = int32 [i1 + 1] segment starts, C2 = int32
                          [M * i0] token of each sorted position, ws = int32 [M * i0] sorted position of (m, j) or -1 (not real);
                          positions of one expert are in token order                                                            */

@@ -1100,6 +1100,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       int tpb = (int)std::min<size_t>(128, (48 * 1024) / ((size_t)o.N * 8));
       if (tpb < 1) return fail("router: too many experts");
       if (tpb >= 32) tpb &= ~31;
+      if (o.ws && (o.M != 1 || o.i0 > 16 || !o.p0 || !o.p1 || o.K < 0)) return fail("router: grouping in the same launch takes one token with at most 16 choices");
       fq3s_router_kernel<<<(o.M + tpb - 1) / tpb, tpb, (size_t)o.N * tpb * 8, s>>>(o);
       return 0;
     }

@@ -619,11 +619,8 @@ __global__ void __launch_bounds__(128) fq3s_lru_scan_kernel(const fq3c_op o, con
 // ---------------------------------------------------------------------------------------------------------------------------
 // Router: one thread per token, its scores in shared memory [n][threads].
 // ---------------------------------------------------------------------------------------------------------------------------
-__global__ void fq3s_router_kernel(const fq3c_op o) {
-  extern __shared__ float rsm[];
-  const int tpb = blockDim.x, n = o.N, tx = threadIdx.x;
-  const int m = blockIdx.x * tpb + tx;
-  if (m >= o.M) return;
+__device__ __forceinline__ void router_token(const fq3c_op& o, const int m, float* rsm, const int tpb, const int tx) {
+  const int n = o.N;
   float* s = rsm + tx;                       // s[i * tpb]
   float* ch = rsm + (size_t)n * tpb + tx;    // choice scores
   const float* z = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
@@ -670,6 +667,34 @@ __global__ void fq3s_router_kernel(const fq3c_op o) {
   }
   const float sc = o.f0 / (wsum + 1e-20f);
   for (int k = 0; k < o.i0; ++k) wt[k] *= sc;
+}
+// With ws / p0 / p1 set (a single token, at most 16 choices, K = experts that have tensors) the launch also does the grouping
+// by expert that fq3s_moe_sort_kernel does for many tokens: segment starts -> p0, rows -> p1, each choice's place -> ws.
+__global__ void fq3s_router_kernel(const fq3c_op o) {
+  extern __shared__ float rsm[];
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m < o.M) router_token(o, m, rsm, blockDim.x, threadIdx.x);
+  if (!o.ws) return;
+  __syncthreads();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int E = o.K, top = o.i0, n = min(16, o.M * top);
+  int* seg = const_cast<int*>(reinterpret_cast<const int*>(o.p0));
+  int* rows = const_cast<int*>(reinterpret_cast<const int*>(o.p1));
+  int* pos = reinterpret_cast<int*>(o.ws);
+  int lid[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) lid[i] = i < n ? reinterpret_cast<const int*>(o.C)[i] : 0x7fffffff;
+  int run = 0;
+  for (int e = 0; e < E; ++e) {
+    seg[e] = run;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (lid[i] == e) { rows[run] = i / top; pos[i] = run; ++run; }
+  }
+  seg[E] = run;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    if (i < n && lid[i] >= E) pos[i] = -1;
 }
 
 // One block.  Counting sort of the (token, choice) pairs by expert, token order kept inside an expert.

@@ -106,8 +106,8 @@ class StepBuilder:
         f32 = w.dtype == torch.float32
         assert x.dtype == w.dtype, (x.dtype, w.dtype)
         flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_GELU if gelu else 0) | (F_F32 if f32 else 0)
-        if out.dtype == torch.float32:
-            flags |= F_NOROUND
+        if out.dtype == torch.float32 or M <= 4:
+            flags |= F_NOROUND      # f32 results stay unrounded; with a few rows the flag also picks the weight-streaming product
         kw = dict(M=M, N=N, K=K, taps=1, cin=K, a_rows=x.shape[0], lda=x.shape[1], ldc=out.shape[1], col_mod=N, A=x, B=w, C=out, flags=flags)
         if bias is not None:
             kw["bias"] = bias
@@ -192,11 +192,14 @@ class StepBuilder:
         kw = dict(M=M, N=n, i0=top, i1=c.groups, i2=c.keep, f0=c.scale, A=z, lda=n, C=ids, C2=wt)
         if w.get("correction") is not None:
             kw["bias"] = w["correction"]
-        self._op(K_ROUTER, **kw)
         seg = self.buf("moe.seg", 1, E + 1, torch.int32)
         rows = self.buf("moe.rows", 1, M * top, torch.int32)
         pos = self.buf("moe.pos", M, top, torch.int32)
-        self._op(K_MOE_SORT, M=M, i0=top, i1=E, A=ids, C=seg, C2=rows, ws=pos)
+        if M == 1 and top <= 16:       # a single token: the router's launch also groups its choices by expert
+            self._op(K_ROUTER, K=E, p0=seg, p1=rows, ws=pos, **kw)
+        else:
+            self._op(K_ROUTER, **kw)
+            self._op(K_MOE_SORT, M=M, i0=top, i1=E, A=ids, C=seg, C2=rows, ws=pos)
         ff = c.expert_ff
         f32 = xop.dtype == torch.float32
         act = self.buf("moe.act", M * top, ff, self.adt)
