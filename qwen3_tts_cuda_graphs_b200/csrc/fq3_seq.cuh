@@ -355,6 +355,28 @@ __global__ void __launch_bounds__(256) fq3s_gemm_mma128_kernel(const SeqGemm g) 
       }
 }
 
+// K values of a row into shared memory as f32: 16-byte loads when the row allows them (one round trip for a few thousand values
+// instead of one per 256), else one value per thread and round.
+template <typename TA>
+__device__ __forceinline__ void stage_row_f32(float* dst, const TA* src, const int K, const int tid, const int nth) {
+  constexpr int V = 16 / sizeof(TA);
+  if (((reinterpret_cast<uintptr_t>(src) & 15) == 0) && (K % V == 0)) {
+    for (int i = tid; i < K / V; i += nth) {
+      const uint4 r = __ldg(reinterpret_cast<const uint4*>(src) + i);
+      float* d = dst + i * V;
+      if (sizeof(TA) == 2) {
+        const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { d[(2 * q) % V] = __uint_as_float(u[q] << 16); d[(2 * q + 1) % V] = __uint_as_float(u[q] & 0xffff0000u); }
+      } else {
+        d[0] = __uint_as_float(r.x); d[1] = __uint_as_float(r.y); d[2 % V] = __uint_as_float(r.z); d[3 % V] = __uint_as_float(r.w);
+      }
+    }
+  } else {
+    for (int i = tid; i < K; i += nth) dst[i] = ldf<TA>(src + i);
+  }
+}
+
 // One output row with few rows in flight (decode: M <= 8): a warp per output column streams its weight row once, 16 bytes per
 // lane and load, and dots it with every A row (f32 or bf16 in shared memory as f32).  Weight-streaming bound.
 template <typename TA, typename TB>
@@ -378,10 +400,7 @@ __global__ void __launch_bounds__(256) fq3s_gemv_kernel(const SeqGemm g) {
       raw[u] = k < g.K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0u, 0u, 0u, 0u);
     }
   }
-  for (int i = threadIdx.x; i < g.M * g.K; i += blockDim.x) {
-    const int m = i / g.K, k = i - m * g.K;
-    xs[i] = ldf<TA>(Ap + (size_t)m * g.lda + k);
-  }
+  for (int m = 0; m < g.M; ++m) stage_row_f32<TA>(xs + (size_t)m * g.K, Ap + (size_t)m * g.lda, g.K, threadIdx.x, blockDim.x);
   __syncthreads();
   if (n >= g.N) return;
   float acc[8];
@@ -454,7 +473,7 @@ __global__ void __launch_bounds__(256) fq3s_ggemv_kernel(const SeqGemm g) {
   if (e >= g.E) return;          // beyond the last segment: choices without tensors (identity experts) leave fewer rows
   const int arow = g.rows ? g.rows[p] : p;
   const TA* a = reinterpret_cast<const TA*>(g.A) + (size_t)arow * g.lda;
-  for (int i = threadIdx.x; i < g.K; i += blockDim.x) xs[i] = ldf<TA>(a + i);
+  stage_row_f32<TA>(xs, a, g.K, threadIdx.x, blockDim.x);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 8 + warp;
@@ -463,18 +482,29 @@ __global__ void __launch_bounds__(256) fq3s_ggemv_kernel(const SeqGemm g) {
   float acc = 0.f;
   constexpr int VEC = 16 / sizeof(TB);
   if (((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (g.K % VEC == 0)) {
-    for (int k = lane * VEC; k < g.K; k += 32 * VEC) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
-      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
-      if (sizeof(TB) == 2) {
+    for (int k0 = lane * VEC; k0 < g.K; k0 += 4 * 32 * VEC) {      // four 16-byte loads in flight per lane
+      uint4 raw[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          acc = fmaf(__uint_as_float(u[q] << 16), xs[k + 2 * q], acc);
-          acc = fmaf(__uint_as_float(u[q] & 0xffff0000u), xs[k + 2 * q + 1], acc);
+      for (int b = 0; b < 4; ++b) {
+        const int k = k0 + b * 32 * VEC;
+        raw[b] = k < g.K ? __ldg(reinterpret_cast<const uint4*>(w + k)) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int k = k0 + b * 32 * VEC;
+        if (k < g.K) {
+          const uint32_t u[4] = {raw[b].x, raw[b].y, raw[b].z, raw[b].w};
+          if (sizeof(TB) == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc = fmaf(__uint_as_float(u[q] << 16), xs[k + 2 * q], acc);
+              acc = fmaf(__uint_as_float(u[q] & 0xffff0000u), xs[k + 2 * q + 1], acc);
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc = fmaf(__uint_as_float(u[q]), xs[k + q], acc);
+          }
         }
-      } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) acc = fmaf(__uint_as_float(u[q]), xs[k + q], acc);
       }
     }
   } else {
