@@ -52,10 +52,11 @@ enum fq3c_kind {
   FQ3C_TCONV = 13,    /* causal per-channel convolution over time with carried inputs: C[m, c] = (RESID ? A[m, c] : 0) + bias[c] +
                          sum_j B(f32 [N, taps])[c, j] * in[m - (taps - 1) + j, c], where rows before this call come from the history
                          p0 (f32 [taps - 1, N], oldest first; zeros at a sequence's start).  The next history (the last taps - 1
-                         inputs) is written to p1 (f32 [taps - 1, N]); FQ3C_COMMIT installs it.                                */
+                         inputs) is written to p1 (f32 [taps - 1, N]); FQ3C_COMMIT installs it.  FQ3C_SILU (ABI 7): silu of the result. */
   FQ3C_GNORM = 14,    /* RMS norm in i0 equal consecutive groups, eps f0, times scale (f32 [N]); RESID: C = res (f32 [M, ldr]) +
                          that (res may be C).  C2, when given: the bf16 rounding of the same result.  p0, when given (device int32):
-                         output row m is row *p0 + m of C (cache append)                                                       */
+                         output row m is row *p0 + m of C (cache append).  i2 > 0 (ABI 7): the weights repeat with period i2
+                         (one weight vector shared by equal parts).  FQ3C_GATE_PRE / FQ3C_GATE_POST: a silu gate p1 (f32, pitch i1)     */
   FQ3C_BDGEMM = 15,   /* block-diagonal product: i0 blocks of [i2 out, cin in]; C[m, b * i2 + n] = epi(sum_k A[m, (b % i1) * cin + k] *
                          B[b][n][k] + bias[b * i2 + n]); N = i0 * i2.  Flags: BIAS, SIGMOID, OUT_F32, F32 (B is f32)              */
   FQ3C_LATENT_ATTN = 16, /* attention over a cache of shared latent rows in absorbed form: A = queries already projected into latent
@@ -86,8 +87,44 @@ enum fq3c_kind {
   FQ3C_MOE_COMBINE = 22, /* C f32 [M, N] = sum_j w[m, j] * (ids[m, j] >= i1 ? x[m, :] : Y[pos[m, j], :]) (+ res[m, :]);
                          A = Y f32, B = x f32 [M, ldr] (identity experts), p0 = ids int32 [M, i0], p1 = w f32 [M, i0],
                          ws = pos int32 [M, i0], res = f32 [M, ldr] or NULL (shared expert)                                      */
-  FQ3C_COMMIT = 23    /* end of a step: A = device int64 [M, 3] rows (dst, src, bytes), bytes a multiple of 4, copied in one launch;
+  FQ3C_COMMIT = 23,   /* end of a step: A = device int64 [M, 3] rows (dst, src, bytes), bytes a multiple of 4, copied in one launch;
                          then *(int32*)C += i0 (the sequence's position counter)                                               */
+  /* ---- ABI 7: more mechanisms of the sequence models (same conventions as kinds 12-23) */
+  FQ3C_DYT = 24,      /* dynamic-tanh norm (no statistics): C[m, c] = tanh(f0 * A[m, c]) * scale[c] + bias[c] (bias may be NULL);
+                         RESID: C = res (f32 [M, ldr]) + that (res may be C).  C2, when given: the bf16 rounding of the result.
+                         With norm_out set, a second norm of the finished row is written too: norm_out[m, c] (bf16; f32 with
+                         FQ3C_F32; pitch norm_ld) = tanh(norm_eps * C[m, c]) * norm_w[c] + norm_w[N + c]                           */
+  FQ3C_DEPTH_MIX = 25,/* weighted sum over depth: C f32 [M, N] = sum_(j < i0) p0[j] * A_j[m, :], A_j = A + j * K elements (f32 slices
+                         [M, lda] of one buffer), p0 = f32 [i0] on the device.  C2 (bf16 copy) and norm_out as in FQ3C_DYT              */
+  FQ3C_XIELU = 26,    /* C[m, c] = z > 0 ? softplus(p0[0]) z^2 + z / 2 : (1/2 + softplus(p0[1])) (exp(z) - 1 - z) + z / 2, z = A[m, c];
+                         p0 = f32 [2] on the device                                                                               */
+  FQ3C_ROT_APPEND = 27, /* rotary positions and cache append for softmax attention.  A = f32 rows [M, lda] holding i0 query heads of
+                         size i2 at column 0, i1 key heads of size i2 at column K and i1 value heads of size cin at column a_rows.
+                         Row m is position *p0 + m.  The first `taps` entries of every query and key head turn in pairs (2i, 2i + 1)
+                         by the angle position * B[i] (B = f32 [taps / 2] frequencies; taps = 0: no rotation); queries in place,
+                         keys into row *p0 + m of the key cache C (pitch ldc), values into the value cache C2 (pitch ldr); caches
+                         bf16, or f32 with FQ3C_F32.  i1 = 0: queries only (a layer that reads another layer's cache)               */
+  FQ3C_CACHE_ATTN = 28, /* softmax attention of M new queries over a key / value cache.  A = queries f32 [M, lda] (i0 heads of size i2),
+                         B = key cache rows [i1 heads * i2] of pitch ldr, p1 = value cache rows [i1 heads * cin] of pitch taps
+                         (bf16, F32: f32); query head h reads key / value head h / (i0 / i1); query m has position i = *p0 + m
+                         and sees j <= i with (K == 0 or i - j < K or j < a_rows): K = window, a_rows = first positions every
+                         query keeps.  score = f0 * q.k; f1 > 0: score <- f1 tanh(score / f1); bias (f32 [2 * i0], r1 then r2), when
+                         given: score -= r1[h] ln(1 + r2[h] (i - j)); scale (f32 [i0]), when given: a per-head sink that only adds
+                         exp(scale[h]) to the softmax denominator; res (f32 [M, col_mod]), when given: head h's output is multiplied
+                         by sigmoid(res[m, h]).  C [M, i0 * cin].  m_begin = key-range splits (> 1: ws holds the partial states and
+                         a second launch merges them)                                                                              */
+  FQ3C_MSTATE_SCAN = 29 /* recurrences whose state is a matrix S [i2, cin] per head (i0 heads, i1 key groups; head h reads group
+                         h / (i0 / i1)), 32-bit.  A = f32 rows [M, lda] after the short convolution: taps = 0 (gated delta rule):
+                         queries of group g at column g * i2, keys at column K + g * i2, values of head h at a_rows + h * cin;
+                         taps = 1 (state-space scan): x of head h at column h * cin, B of group g at K + g * i2, C at a_rows + g * i2.
+                         res = f32 rows [M, ldr] with the raw per-head projections: col_mod = column of the decay input (a / dt),
+                         m_begin = column of the write-strength input (delta rule only).  scale = A_log f32 [i0], bias = dt_bias
+                         f32 [i0], B = D f32 [i0] (scan only).
+                           delta rule: q, k <- unit vectors (x / sqrt(sum x^2 + 1e-6)), q *= i2^(-1/2); beta = sigmoid(b);
+                             g = exp(-exp(A_log) softplus(a + dt_bias));  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+                           scan: dt = softplus(dt + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
+                         State read from p0 (f32 [i0, i2, cin]), next state written to C2 (FQ3C_COMMIT installs it); C f32 [M, i0 * cin];
+                         ws = f32 [M, 2 * i0 + (taps == 0 ? 2 * i1 * i2 : 0)] for the per-token coefficients (and unit vectors)       */
 };
 
 enum fq3c_flags {
@@ -99,7 +136,10 @@ enum fq3c_flags {
   FQ3C_NOROUND = 1024   /* GEMM with OUT_F32: the accumulator is not rounded to bf16 on its way out */,
   FQ3C_GELU_TANH = 2048 /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */,
   FQ3C_SIGMOID = 4096,
-  FQ3C_A_F32 = 8192     /* GGEMM: A rows are f32 while B is bf16 */
+  FQ3C_A_F32 = 8192     /* GGEMM: A rows are f32 while B is bf16 */,
+  /* ABI 7 */
+  FQ3C_GATE_PRE = 16384 /* GNORM: the row is multiplied by silu(p1[m, c]) (f32, pitch i1) before its statistics are taken */,
+  FQ3C_GATE_POST = 32768 /* GNORM: the normed, weighted row is multiplied by silu(p1[m, c]) */
 };
 
 typedef struct fq3c_op {

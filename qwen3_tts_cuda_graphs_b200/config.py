@@ -332,9 +332,120 @@ class SidalornConfig:
                               int(canon.get("taps", 0)), tuple(layers))
 
 
+@dataclass(frozen=True)
+class SoftmaxAttentionConfig:
+    """Softmax attention over a per-sequence key / value cache with grouped key / value heads.  Every option is a parameter:
+    partial interleaved rotary positions, a tanh cap on the scores, a sliding window that also keeps the first positions, a
+    logarithmic distance penalty per head, a per-head sink in the denominator, a per-head sigmoid output gate, projection
+    biases, and reading another layer's cache instead of projecting keys and values."""
+
+    heads: int
+    kv_heads: int
+    dim: int                 # query / key size per head
+    vdim: int                # value size per head
+    scale: float             # multiplies q . k
+    softcap: float = 0.0     # > 0: score <- softcap * tanh(score / softcap)
+    rot_dims: int = 0        # leading entries of each head that turn with the position (pairs 2i, 2i + 1); 0: no rotation
+    rot_base: float = 10000.0
+    window: int = 0          # > 0: position i sees j only if i - j < window ...
+    keep_first: int = 0      # ... or j < keep_first
+    sink: bool = False
+    gate: bool = False       # one sigmoid gate per head on the head's output
+    bias: bool = False       # q, k, v and output projections have biases
+    distance: bool = False   # score -= r1_h ln(1 + r2_h (i - j))
+    kv_from: Optional[int] = None   # index of the layer whose cached keys / values this layer reads
+
+
+@dataclass(frozen=True)
+class DeltaRuleConfig:
+    """Gated delta rule: a [dim, vdim] state per head, decayed, corrected towards the new value along the new key, read by the query."""
+
+    heads: int
+    kv_heads: int            # query / key heads
+    dim: int
+    vdim: int
+    conv: int                # taps of the causal convolution on q, k, v
+
+
+@dataclass(frozen=True)
+class StateSpaceConfig:
+    """State-space scan with a scalar decay per head (the dual form of a linear attention): state [state, vdim] per head."""
+
+    heads: int
+    vdim: int
+    state: int
+    groups: int              # B / C groups
+    conv: int
+    norm_groups: int
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+
+@dataclass(frozen=True)
+class ParallelMixerConfig:
+    """Two mixers reading the same input; the result is half the sum of their unit-RMS, weighted outputs."""
+
+    left: SoftmaxAttentionConfig
+    right: StateSpaceConfig
+
+
+@dataclass(frozen=True)
+class RedodraConfig:
+    """Redodra: dynamic-tanh norms before and after every sublayer, a learned weighted sum over the outputs of all earlier layers
+    after every layer, delta-rule / gated sink attention / (windowed attention + state-space scan) mixers in a configured order,
+    xIELU dense feed-forwards."""
+
+    architecture = "Redodra"
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: Tuple[SeqLayerConfig, ...]
+
+    @staticmethod
+    def _attention(m: dict, **kw) -> SoftmaxAttentionConfig:
+        rot = m.get("rot") or {}
+        mask = m.get("mask") or {}
+        return SoftmaxAttentionConfig(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), float(m["scale"]),
+                                      float(m.get("softcap") or 0.0), int(rot.get("dims", 0)), float(rot.get("base", 10000.0)),
+                                      int(mask.get("size", 0)), int(mask.get("keep_first", 0)), kv_from=m.get("kv_from"), **kw)
+
+    @staticmethod
+    def from_dict(raw: dict) -> "RedodraConfig":
+        layers = []
+        for i, L in enumerate(raw["layers"]):
+            m = L["mixer"]
+            if L["type"] == "delta":
+                mixer = DeltaRuleConfig(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m["conv"]))
+            elif L["type"] == "attention":
+                mixer = RedodraConfig._attention(m, sink=True, gate=True)
+                j = mixer.kv_from
+                if j is not None and not (0 <= int(j) < i and raw["layers"][int(j)]["type"] == "attention"
+                                          and raw["layers"][int(j)]["mixer"].get("kv_from") is None):
+                    raise ValueError(f"layer {i}: kv_from must name an earlier attention layer with projections of its own")
+            elif L["type"] == "parallel":
+                r = m["right"]
+                mixer = ParallelMixerConfig(RedodraConfig._attention(m["left"], bias=True, distance=True),
+                                            StateSpaceConfig(int(r["heads"]), int(r["vdim"]), int(r["state"]), int(r["groups"]), int(r["conv"]),
+                                                             int(r.get("norm_groups", 1))))
+            else:
+                raise ValueError(f"unknown mixer type {L['type']!r}")
+            f = L.get("mlp")
+            if f is None:
+                mlp = None
+            elif f["kind"] == "dense":
+                mlp = DenseFFConfig(int(f["ff"]))
+            else:
+                raise ValueError(f"unknown feed-forward kind {f['kind']!r}")
+            layers.append(SeqLayerConfig(L["type"], mixer, mlp))
+        return RedodraConfig(int(raw["vocab"]), int(raw["width"]), float((raw.get("norm") or {}).get("eps", 1e-6)), tuple(layers))
+
+
 # config.json "architecture" -> (config class, "module:class" of the model that lowers it to op lists)
 SEQUENCE_ARCHITECTURES = {
     "Sidalorn": (SidalornConfig, "sidalorn:SidalornModel"),
+    "Redodra": (RedodraConfig, "redodra:RedodraModel"),
 }
 
 

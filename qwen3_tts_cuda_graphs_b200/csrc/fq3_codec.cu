@@ -1057,6 +1057,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       return 0;
     case FQ3C_GNORM:
       if (o.i0 < 1 || o.N % o.i0 || !o.scale || ((o.flags & FQ3C_RESID) && !o.res)) return fail("gnorm: groups must divide N; weights required");
+      if ((o.flags & (FQ3C_GATE_PRE | FQ3C_GATE_POST)) && !o.p1) return fail("gnorm: gate rows required");
       fq3s_gnorm_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o);
       return 0;
     case FQ3C_POLYNORM:
@@ -1181,6 +1182,68 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       }
       return 0;
     }
+    case FQ3C_DYT:
+      if (!o.A || !o.scale || !o.C || ((o.flags & FQ3C_RESID) && !o.res)) return fail("dyt: missing operand");
+      if (o.norm_out && (!o.norm_w || !(o.flags & FQ3C_OUT_F32))) return fail("dyt: a chained norm needs its weights and an f32 result");
+      fq3s_dyt_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_DEPTH_MIX:
+      if (o.i0 < 1 || !o.A || !o.p0 || !o.C || (o.norm_out && !o.norm_w)) return fail("depth_mix: missing operand");
+      fq3s_depth_mix_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_XIELU:
+      if (!o.A || !o.p0 || !o.C) return fail("xielu: missing operand");
+      fq3s_xielu_kernel<<<dim3((o.N + 255) / 256, o.M), 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_ROT_APPEND:
+      if (!o.A || o.i0 < 0 || o.i1 < 0 || o.i2 < 1 || o.taps < 0 || (o.taps & 1) || o.taps > o.i2 || (o.taps > 0 && !o.B) || (o.i1 > 0 && (!o.C || !o.C2)))
+        return fail("rot_append: bad configuration");
+      if (o.flags & FQ3C_F32) fq3s_rot_append_kernel<float><<<o.M, 256, 0, s>>>(o);
+      else fq3s_rot_append_kernel<bf16><<<o.M, 256, 0, s>>>(o);
+      return 0;
+    case FQ3C_CACHE_ATTN: {
+      if (o.i0 < 1 || o.i1 < 1 || o.i0 % o.i1 || o.i2 < 1 || o.cin < 1 || !o.A || !o.B || !o.p1 || !o.C) return fail("cache_attn: bad configuration");
+      const int splits = std::max(1, o.m_begin), HG = o.i0 / o.i1;
+      if (splits > 64) return fail("cache_attn: at most 64 key splits");
+      if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.cin + 2) * 4)) return fail("cache_attn: workspace too small for the splits");
+      int QB = o.M == 1 ? 1 : std::max(1, std::min(std::min(16, o.M), 16 / HG)), TJ = 32;
+      while (cache_attn_smem(QB * HG, TJ, o.i2, o.cin) > 200 * 1024 && QB > 1) QB >>= 1;
+      while (cache_attn_smem(QB * HG, TJ, o.i2, o.cin) > 200 * 1024 && TJ > 4) TJ >>= 1;
+      const size_t smem = cache_attn_smem(QB * HG, TJ, o.i2, o.cin);
+      if (smem > 200 * 1024) return fail("cache_attn: heads too large for shared memory");
+      static bool attr[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !attr[dev]) {
+        cudaFuncSetAttribute(fq3s_cache_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(fq3s_cache_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr[dev] = true;
+      }
+      dim3 grid((o.M + QB - 1) / QB, o.i1, splits);
+      if (o.flags & FQ3C_F32) fq3s_cache_attn_kernel<float><<<grid, 256, smem, s>>>(o, QB, TJ, splits);
+      else fq3s_cache_attn_kernel<bf16><<<grid, 256, smem, s>>>(o, QB, TJ, splits);
+      if (splits > 1) {
+        fq3s_cache_attn_merge_kernel<<<dim3(o.M, o.i0), 128, 0, s>>>(o, splits);
+        count_launches(1);
+      }
+      return 0;
+    }
+    case FQ3C_MSTATE_SCAN: {
+      if (o.i0 < 1 || o.i1 < 1 || o.i0 % o.i1 || o.i2 < 1 || o.cin < 1 || !o.A || !o.res || !o.scale || !o.p0 || !o.C || !o.C2 || !o.ws)
+        return fail("mstate_scan: bad configuration");
+      if (o.taps != 0 && o.taps != 1) return fail("mstate_scan: taps selects the delta rule (0) or the state-space scan (1)");
+      if (o.ws_bytes < (int64_t)o.M * mstate_ws_cols(o.i0, o.i1, o.i2, o.taps == 0) * 4) return fail("mstate_scan: workspace too small");
+      if (o.i2 > 256) return fail("mstate_scan: at most 256 state rows per head");
+      fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
+      count_launches(1);
+      dim3 grid((o.cin + 31) / 32, o.i0);
+      const size_t smem = sizeof(float) * ((size_t)MS_CH * 2 * o.i2 + MS_CH * 32 + MS_CH * 2);
+      if (o.i2 <= 32) fq3s_mstate_scan_kernel<8><<<grid, 128, smem, s>>>(o);
+      else if (o.i2 <= 64) fq3s_mstate_scan_kernel<16><<<grid, 128, smem, s>>>(o);
+      else if (o.i2 <= 128) fq3s_mstate_scan_kernel<32><<<grid, 128, smem, s>>>(o);
+      else fq3s_mstate_scan_kernel<64><<<grid, 128, smem, s>>>(o);
+      return 0;
+    }
     default: return 1;
   }
 }
@@ -1189,7 +1252,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
 
 extern "C" {
 
-int fq3c_abi_version(void) { return 6; }
+int fq3c_abi_version(void) { return 7; }
 const char* fq3c_last_error(void) { return g_err.c_str(); }
 int64_t fq3c_launch_count(void) { return g_launches.load(); }
 

@@ -1,4 +1,4 @@
-// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-23): the pieces a decoder-only
+// fq3_seq.cuh — sequence-model ops of the op-list interpreter (include/fq3_codec.h, kinds 12-29): the pieces a decoder-only
 // language model with a 32-bit residual stream is lowered to.  Included by fq3_codec.cu inside its anonymous namespace.
 //
 // What is 32-bit here whatever the weights' type: norms, softmax scores and weights, router, recurrent state and everything that
@@ -7,6 +7,8 @@
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -551,23 +553,35 @@ __global__ void __launch_bounds__(256) fq3s_tconv_kernel(const fq3c_op o) {
     a = fmaf(w[j], v, a);
   }
   if (o.flags & FQ3C_RESID) a += x[(size_t)m * o.lda + c];
+  if (o.flags & FQ3C_SILU) a = a / (1.f + expf(-a));
   if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + c] = a;
   else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(a);
 }
 
-// grid (M, groups); one block per (row, group)
+// grid (M, groups); one block per (row, group).  An optional silu gate (p1, pitch i1) multiplies the row before the statistics
+// (FQ3C_GATE_PRE) or the finished row (FQ3C_GATE_POST); weights repeat with period i2 when i2 > 0.
 __global__ void __launch_bounds__(128) fq3s_gnorm_kernel(const fq3c_op o) {
   __shared__ float red[32];
   const int m = blockIdx.x, gsz = o.N / o.i0, c0 = blockIdx.y * gsz;
   const float* x = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + c0;
+  const bool pre = (o.flags & FQ3C_GATE_PRE) != 0, post = (o.flags & FQ3C_GATE_POST) != 0;
+  const float* gate = (pre || post) ? reinterpret_cast<const float*>(o.p1) + (size_t)m * o.i1 + c0 : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < gsz; i += blockDim.x) { const float v = x[i]; ss = fmaf(v, v, ss); }
+  for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
+    float v = x[i];
+    if (pre) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
+    ss = fmaf(v, v, ss);
+  }
   ss = seq_block_sum(ss, red);
   const float rs = 1.f / sqrtf(ss / (float)gsz + o.f0);
-  const float* w = reinterpret_cast<const float*>(o.scale) + c0;
+  const float* w = reinterpret_cast<const float*>(o.scale);
+  const int wmod = o.i2 > 0 ? o.i2 : o.N;
   const size_t orow = (size_t)m + (o.p0 ? (size_t)*reinterpret_cast<const int*>(o.p0) : 0);
   for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
-    float v = x[i] * rs * w[i];
+    float v = x[i];
+    if (pre) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
+    v = v * rs * w[(c0 + i) % wmod];
+    if (post) { const float z = gate[i]; v *= z / (1.f + expf(-z)); }
     if (o.flags & FQ3C_RESID) v += reinterpret_cast<const float*>(o.res)[(size_t)m * o.ldr + c0 + i];
     if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[orow * o.ldc + c0 + i] = v;
     else reinterpret_cast<bf16*>(o.C)[orow * o.ldc + c0 + i] = __float2bfloat16_rn(v);
@@ -1128,4 +1142,374 @@ __global__ void __launch_bounds__(256) fq3s_latent_attn_mma_kernel(const fq3c_op
         if (nt < nt_o) { dst[2 + c0 + nt * 8 + t * 2] = oacc[nt][half * 2]; dst[2 + c0 + nt * 8 + t * 2 + 1] = oacc[nt][half * 2 + 1]; }
     }
   }
+}
+
+// ===========================================================================================================================
+// ABI 7 (kinds 24-29): dynamic-tanh norm, depth mix, xIELU, rotary cache append, cached softmax attention with windows / sinks /
+// distance penalties / output gates, and recurrences with a matrix state per head (gated delta rule, state-space scan).
+// ===========================================================================================================================
+
+// what follows a finished f32 value of the residual stream: the stream itself, its bf16 copy, and the next norm's output
+__device__ __forceinline__ void stream_out(const fq3c_op& o, const int m, const int c, const float v) {
+  reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + c] = v;
+  if (o.C2) reinterpret_cast<bf16*>(o.C2)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(v);
+  if (o.norm_out) {
+    const float* w = reinterpret_cast<const float*>(o.norm_w);
+    const float n = fmaf(tanhf(o.norm_eps * v), w[c], w[o.N + c]);
+    if (o.flags & FQ3C_F32) reinterpret_cast<float*>(o.norm_out)[(size_t)m * o.norm_ld + c] = n;
+    else reinterpret_cast<bf16*>(o.norm_out)[(size_t)m * o.norm_ld + c] = __float2bfloat16_rn(n);
+  }
+}
+
+// grid (ceil(N / 256), M)
+__global__ void __launch_bounds__(256) fq3s_dyt_kernel(const fq3c_op o) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+  if (c >= o.N) return;
+  float v = tanhf(o.f0 * reinterpret_cast<const float*>(o.A)[(size_t)m * o.lda + c]) * reinterpret_cast<const float*>(o.scale)[c];
+  if (o.bias) v += reinterpret_cast<const float*>(o.bias)[c];
+  if (o.flags & FQ3C_RESID) v += reinterpret_cast<const float*>(o.res)[(size_t)m * o.ldr + c];
+  if (o.flags & FQ3C_OUT_F32) stream_out(o, m, c, v);
+  else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(v);
+}
+
+// grid (ceil(N / 256), M)
+__global__ void __launch_bounds__(256) fq3s_depth_mix_kernel(const fq3c_op o) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+  if (c >= o.N) return;
+  const float* a = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda + c;
+  const float* w = reinterpret_cast<const float*>(o.p0);
+  float v = 0.f;
+  for (int j = 0; j < o.i0; ++j) v = fmaf(w[j], a[(size_t)j * (size_t)o.K], v);
+  stream_out(o, m, c, v);
+}
+
+// grid (ceil(N / 256), M)
+__global__ void __launch_bounds__(256) fq3s_xielu_kernel(const fq3c_op o) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+  if (c >= o.N) return;
+  const float* p = reinterpret_cast<const float*>(o.p0);
+  const float ap = softplus_f(p[0]), aq = 0.5f + softplus_f(p[1]);
+  const float z = reinterpret_cast<const float*>(o.A)[(size_t)m * o.lda + c];
+  const float v = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+  if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + c] = v;
+  else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + c] = __float2bfloat16_rn(v);
+}
+
+// grid (M), 256 threads.  Angles in f32: position (exact as a float below 2^24) times the frequency, full-range sincosf.
+template <typename TC>
+__global__ void __launch_bounds__(256) fq3s_rot_append_kernel(const fq3c_op o) {
+  const int m = blockIdx.x, H = o.i0, G = o.i1, d = o.i2, dv = o.cin, half = o.taps >> 1;
+  const int pos = (o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0) + m;
+  float* row = const_cast<float*>(reinterpret_cast<const float*>(o.A)) + (size_t)m * o.lda;
+  const float* freq = reinterpret_cast<const float*>(o.B);
+  const float fp = (float)pos;
+  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    float sn, cs;
+    sincosf(fp * freq[i], &sn, &cs);
+    float* e = row + (size_t)h * d + 2 * i;
+    const float a = e[0], b = e[1];
+    e[0] = a * cs - b * sn;
+    e[1] = b * cs + a * sn;
+  }
+  if (G <= 0) return;
+  TC* kc = reinterpret_cast<TC*>(o.C) + (size_t)pos * o.ldc;
+  TC* vc = reinterpret_cast<TC*>(o.C2) + (size_t)pos * o.ldr;
+  const float* k = row + o.K;
+  const float* v = row + o.a_rows;
+  for (int idx = threadIdx.x; idx < G * half; idx += blockDim.x) {
+    const int g = idx / half, i = idx - g * half;
+    float sn, cs;
+    sincosf(fp * freq[i], &sn, &cs);
+    const float a = k[(size_t)g * d + 2 * i], b = k[(size_t)g * d + 2 * i + 1];
+    stf(kc + (size_t)g * d + 2 * i, a * cs - b * sn);
+    stf(kc + (size_t)g * d + 2 * i + 1, b * cs + a * sn);
+  }
+  const int rest = d - 2 * half;
+  for (int idx = threadIdx.x; idx < G * rest; idx += blockDim.x) {
+    const int g = idx / rest, c = 2 * half + idx - g * rest;
+    stf(kc + (size_t)g * d + c, k[(size_t)g * d + c]);
+  }
+  for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) stf(vc + idx, v[idx]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Softmax attention over a key / value cache on the CUDA cores, every sum in f32.  A block takes QB consecutive queries x the HG
+// query heads of one key / value head (R = QB * HG rows that score the same staged key tile), 256 threads, online softmax over
+// tiles of TJ keys; tiles that no row of the block can see (outside the window and beyond the kept first positions) are skipped.
+// grid (ceil(M / QB), key heads, splits).  One split finishes in place (sink, output gate); several leave (max, sum, out) per
+// (row, split) in ws for fq3s_cache_attn_merge_kernel.
+// Shared memory (f32): q [R][d], keys [TJ][d + 1], values [TJ][dv], p [R][TJ], out [R][dv], max / sum / rescale [3][R].
+// ---------------------------------------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t cache_attn_smem(int R, int TJ, int d, int dv) {
+  return sizeof(float) * ((size_t)R * d + (size_t)TJ * (d + 1) + (size_t)TJ * dv + (size_t)R * TJ + (size_t)R * dv + 3 * (size_t)R);
+}
+struct CacheAttnMask {
+  int window, keep;
+  __device__ __forceinline__ bool sees(int i, int j) const { return j <= i && (window <= 0 || i - j < window || j < keep); }
+};
+template <typename TC>
+__global__ void __launch_bounds__(256) fq3s_cache_attn_kernel(const fq3c_op o, const int QB, const int TJ, const int splits) {
+  extern __shared__ float csm[];
+  const int H = o.i0, G = o.i1, d = o.i2, dv = o.cin, HG = H / G, R = QB * HG;
+  const int m0 = blockIdx.x * QB, g = blockIdx.y, z = blockIdx.z;
+  const int nq = min(QB, o.M - m0);
+  float* qs = csm;
+  float* kt = qs + (size_t)R * d;
+  float* vt = kt + (size_t)TJ * (d + 1);
+  float* ps = vt + (size_t)TJ * dv;
+  float* oa = ps + (size_t)R * TJ;
+  float* mx = oa + (size_t)R * dv;
+  float* ls = mx + R;
+  float* al = ls + R;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+  const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
+  const CacheAttnMask mask{o.K, o.a_rows};
+  const int ifirst = P + m0, ilast = P + m0 + nq - 1;
+  const int ntiles = ilast / TJ + 1;
+  const int per = (ntiles + splits - 1) / splits;
+  const int t0 = z * per, t1 = min(ntiles, t0 + per);
+  for (int idx = tid; idx < R * d; idx += blockDim.x) {
+    const int r = idx / d, c = idx - r * d, qi = r / HG, hh = r - qi * HG;
+    qs[idx] = qi < nq ? reinterpret_cast<const float*>(o.A)[(size_t)(m0 + qi) * o.lda + (size_t)(g * HG + hh) * d + c] : 0.f;
+  }
+  for (int idx = tid; idx < R * dv; idx += blockDim.x) oa[idx] = 0.f;
+  for (int idx = tid; idx < R; idx += blockDim.x) { mx[idx] = -INFINITY; ls[idx] = 0.f; }
+  const TC* kc = reinterpret_cast<const TC*>(o.B) + (size_t)g * d;
+  const TC* vc = reinterpret_cast<const TC*>(o.p1) + (size_t)g * dv;
+  const float* r12 = reinterpret_cast<const float*>(o.bias);
+  const float cap = o.f1, icap = o.f1 > 0.f ? 1.f / o.f1 : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const int j0 = t * TJ, jn = min(TJ, ilast + 1 - j0);
+    // nothing of this tile is inside the widest window of the block (that of its first query) nor among the kept positions
+    if (mask.window > 0 && j0 + jn <= ifirst - mask.window + 1 && j0 >= mask.keep) continue;
+    __syncthreads();
+    for (int idx = tid; idx < TJ * d; idx += blockDim.x) {
+      const int jj = idx / d, c = idx - jj * d;
+      kt[(size_t)jj * (d + 1) + c] = jj < jn ? ldf<TC>(kc + (size_t)(j0 + jj) * o.ldr + c) : 0.f;
+    }
+    for (int idx = tid; idx < TJ * dv; idx += blockDim.x) {
+      const int jj = idx / dv, c = idx - jj * dv;
+      vt[idx] = jj < jn ? ldf<TC>(vc + (size_t)(j0 + jj) * o.taps + c) : 0.f;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < R * TJ; idx += blockDim.x) {
+      const int r = idx / TJ, jj = idx - r * TJ, qi = r / HG, i = ifirst + qi, j = j0 + jj;
+      float s = -INFINITY;
+      if (qi < nq && jj < jn && mask.sees(i, j)) {
+        const float* qv = qs + (size_t)r * d;
+        const float* kv = kt + (size_t)jj * (d + 1);
+        float acc = 0.f;
+        for (int c = 0; c < d; ++c) acc = fmaf(qv[c], kv[c], acc);
+        s = acc * o.f0;
+        if (cap > 0.f) s = cap * tanhf(s * icap);
+        if (r12) {
+          const int h = g * HG + (r - qi * HG);
+          s -= r12[h] * log1pf(r12[H + h] * (float)(i - j));
+        }
+      }
+      ps[idx] = s;
+    }
+    __syncthreads();
+    for (int r = warp; r < R; r += nwarp) {
+      float tm = -INFINITY;
+      for (int jj = lane; jj < TJ; jj += 32) tm = fmaxf(tm, ps[(size_t)r * TJ + jj]);
+      tm = warp_max(tm);
+      const float mo = mx[r], mn = fmaxf(mo, tm);
+      float sum = 0.f;
+      for (int jj = lane; jj < TJ; jj += 32) {
+        const float s = ps[(size_t)r * TJ + jj];
+        const float p = s == -INFINITY ? 0.f : expf(s - mn);
+        ps[(size_t)r * TJ + jj] = p;
+        sum += p;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) {
+        const float a = mo == -INFINITY ? 0.f : expf(mo - mn);     // mn is finite whenever mo is
+        al[r] = a;
+        ls[r] = ls[r] * a + sum;
+        mx[r] = mn;
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < R * dv; idx += blockDim.x) {
+      const int r = idx / dv, c = idx - r * dv;
+      const float* p = ps + (size_t)r * TJ;
+      float acc = oa[idx] * al[r];
+      for (int jj = 0; jj < jn; ++jj) acc = fmaf(p[jj], vt[(size_t)jj * dv + c], acc);
+      oa[idx] = acc;
+    }
+  }
+  __syncthreads();
+  const float* sink = reinterpret_cast<const float*>(o.scale);
+  const float* gate = reinterpret_cast<const float*>(o.res);
+  for (int idx = tid; idx < R * dv; idx += blockDim.x) {
+    const int r = idx / dv, c = idx - r * dv, qi = r / HG, h = g * HG + (r - qi * HG), m = m0 + qi;
+    if (qi >= nq) continue;
+    if (splits > 1) {
+      float* dst = reinterpret_cast<float*>(o.ws) + (((size_t)m * H + h) * splits + z) * (dv + 2);
+      if (c == 0) { dst[0] = mx[r]; dst[1] = ls[r]; }
+      dst[2 + c] = oa[idx];
+      continue;
+    }
+    float f = 1.f, den = ls[r];
+    if (sink) {
+      const float mm = fmaxf(mx[r], sink[h]);
+      f = mx[r] == -INFINITY ? 0.f : expf(mx[r] - mm);
+      den = den * f + expf(sink[h] - mm);
+    }
+    float v = oa[idx] * f / den;
+    if (gate) v *= sigmoid_f(gate[(size_t)m * o.col_mod + h]);
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + (size_t)h * dv + c] = v;
+    else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + (size_t)h * dv + c] = __float2bfloat16_rn(v);
+  }
+}
+
+// grid (M, H), 128 threads
+__global__ void __launch_bounds__(128) fq3s_cache_attn_merge_kernel(const fq3c_op o, const int splits) {
+  __shared__ float wsm[64];
+  __shared__ float red[32];
+  const int m = blockIdx.x, h = blockIdx.y, H = o.i0, dv = o.cin;
+  const float* src = reinterpret_cast<const float*>(o.ws) + ((size_t)m * H + h) * splits * (dv + 2);
+  const float* sink = reinterpret_cast<const float*>(o.scale);
+  float mv = -INFINITY, lv = 0.f;
+  if ((int)threadIdx.x < splits) { mv = src[(size_t)threadIdx.x * (dv + 2)]; lv = src[(size_t)threadIdx.x * (dv + 2) + 1]; }
+  float mm = warp_max(mv);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mm;
+  __syncthreads();
+  mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  if (sink) mm = fmaxf(mm, sink[h]);
+  const float w = mv == -INFINITY ? 0.f : expf(mv - mm);
+  if ((int)threadIdx.x < splits) wsm[threadIdx.x] = w;
+  float den = seq_block_sum(w * lv, red);
+  if (sink) den += expf(sink[h] - mm);
+  const float gate = o.res ? sigmoid_f(reinterpret_cast<const float*>(o.res)[(size_t)m * o.col_mod + h]) : 1.f;
+  const float sc = gate / den;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc = fmaf(wsm[s], src[(size_t)s * (dv + 2) + 2 + c], acc);
+    const float v = acc * sc;
+    if (o.flags & FQ3C_OUT_F32) reinterpret_cast<float*>(o.C)[(size_t)m * o.ldc + (size_t)h * dv + c] = v;
+    else reinterpret_cast<bf16*>(o.C)[(size_t)m * o.ldc + (size_t)h * dv + c] = __float2bfloat16_rn(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Recurrences with a matrix state S [dk, dv] per head.  Two launches: the per-token coefficients (and, for the delta rule, the unit
+// query / key vectors) are computed row-parallel into ws; then one block per (head, 32 state columns) walks the tokens in order.
+// A state column is held by four lanes (dk / 4 entries each, interleaved), so a token costs each lane dk / 4 multiply-adds per
+// product plus two shuffles per reduction; tokens arrive in chunks staged through shared memory.
+// ws row m: [c1[H] | c2[H] | unit q [G * dk] | unit k [G * dk]]  (delta rule: c1 = decay, c2 = write strength; scan: c1 = decay, c2 = dt)
+// ---------------------------------------------------------------------------------------------------------------------------
+__host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) { return 2 * H + (delta ? 2 * G * dk : 0); }
+
+// grid (M), 128 threads
+__global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) {
+  const int m = blockIdx.x, H = o.i0, G = o.i1, dk = o.i2;
+  const bool delta = o.taps == 0;
+  float* w = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_ws_cols(H, G, dk, delta);
+  const float* raw = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr;
+  const float* alog = reinterpret_cast<const float*>(o.scale);
+  const float* dtb = reinterpret_cast<const float*>(o.bias);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float sp = softplus_f(raw[o.col_mod + h] + (dtb ? dtb[h] : 0.f));
+    w[h] = expf(-expf(alog[h]) * sp);
+    w[H + h] = delta ? sigmoid_f(raw[o.m_begin + h]) : sp;
+  }
+  if (!delta) return;
+  const float* row = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const float qs = 1.f / sqrtf((float)dk);
+  for (int v = warp; v < 2 * G; v += nwarp) {
+    const bool isk = v >= G;
+    const int g = isk ? v - G : v;
+    const float* x = row + (isk ? o.K : 0) + (size_t)g * dk;
+    float ss = 0.f;
+    for (int c = lane; c < dk; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    const float f = (1.f / sqrtf(ss + 1e-6f)) * (isk ? 1.f : qs);
+    float* dst = w + 2 * H + (size_t)v * dk;
+    for (int c = lane; c < dk; c += 32) dst[c] = x[c] * f;
+  }
+}
+
+constexpr int MS_CH = 16;     // tokens staged per round
+// grid (ceil(dv / 32), H), 128 threads: thread = (column tid / 4 of the tile, lane-of-four tid % 4)
+template <int RPT>
+__global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) {
+  extern __shared__ float msm[];
+  const int H = o.i0, G = o.i1, dk = o.i2, dv = o.cin, h = blockIdx.y, g = h / (H / G);
+  const bool delta = o.taps == 0;
+  const int wc = mstate_ws_cols(H, G, dk, delta);
+  const int tid = threadIdx.x, sub = tid & 3, col = blockIdx.x * 32 + (tid >> 2);
+  const bool live = col < dv;
+  float* kq = msm;                              // [MS_CH][2][dk]: (k, q) or (B, C)
+  float* vs = kq + (size_t)MS_CH * 2 * dk;      // [MS_CH][32]
+  float* cf = vs + MS_CH * 32;                  // [MS_CH][2]
+  float S[RPT];
+  const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) { const int i = r * 4 + sub; S[r] = (live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
+  const float D = (!delta && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
+  const float* wsb = reinterpret_cast<const float*>(o.ws);
+  const float* rows = reinterpret_cast<const float*>(o.A);
+  const int vcol = (delta ? o.a_rows : 0) + h * dv;
+  for (int t0 = 0; t0 < o.M; t0 += MS_CH) {
+    const int nt = min(MS_CH, o.M - t0);
+    __syncthreads();
+    for (int idx = tid; idx < nt * 2 * dk; idx += blockDim.x) {
+      const int tt = idx / (2 * dk), e = idx - tt * 2 * dk, which = e / dk, c = e - which * dk;
+      float v;
+      if (delta) v = wsb[(size_t)(t0 + tt) * wc + 2 * H + (size_t)((which == 0 ? G : 0) + g) * dk + c];      // k first, then q
+      else v = rows[(size_t)(t0 + tt) * o.lda + (which == 0 ? o.K : o.a_rows) + (size_t)g * dk + c];           // B first, then C
+      kq[idx] = v;
+    }
+    for (int idx = tid; idx < nt * 32; idx += blockDim.x) {
+      const int tt = idx >> 5, c = blockIdx.x * 32 + (idx & 31);
+      vs[idx] = c < dv ? rows[(size_t)(t0 + tt) * o.lda + vcol + c] : 0.f;
+    }
+    for (int idx = tid; idx < nt * 2; idx += blockDim.x) {
+      const int tt = idx >> 1, which = idx & 1;
+      cf[idx] = wsb[(size_t)(t0 + tt) * wc + which * H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* kk = kq + (size_t)tt * 2 * dk;
+      const float* qq = kk + dk;
+      const float c1 = cf[tt * 2], c2 = cf[tt * 2 + 1], v = vs[tt * 32 + (tid >> 2)];
+      float os = 0.f;
+      if (delta) {
+        float ks = 0.f;
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const int i = r * 4 + sub;
+          S[r] *= c1;
+          if (i < dk) ks = fmaf(kk[i], S[r], ks);
+        }
+        ks += __shfl_xor_sync(0xffffffffu, ks, 1);
+        ks += __shfl_xor_sync(0xffffffffu, ks, 2);
+        const float u = c2 * (v - ks);
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const int i = r * 4 + sub;
+          if (i < dk) { S[r] = fmaf(kk[i], u, S[r]); os = fmaf(qq[i], S[r], os); }
+        }
+      } else {
+        const float dx = c2 * v;
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+          const int i = r * 4 + sub;
+          if (i < dk) { S[r] = fmaf(c1, S[r], kk[i] * dx); os = fmaf(qq[i], S[r], os); }
+        }
+      }
+      os += __shfl_xor_sync(0xffffffffu, os, 1);
+      os += __shfl_xor_sync(0xffffffffu, os, 2);
+      if (!delta) os = fmaf(D, v, os);
+      if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = os;
+    }
+  }
+  float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * dk * dv;
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) { const int i = r * 4 + sub; if (live && i < dk) nst[(size_t)i * dv + col] = S[r]; }
 }

@@ -5,9 +5,12 @@ it allocates; the list is handed to `fq3c_run` / replayed as a CUDA graph like t
 with its constants as arguments, so another design composes them differently:
 
   embed, time_conv (causal per-channel convolution with carried inputs), group_norm (RMS norm in groups, optional residual
-  add), linear (tcgen05 GEMM, or the CUDA-core / GEMV product for true 32-bit, decode rows and odd shapes), latent_attention
-  (low-rank shared latent cache, absorbed projections, sink softmax), rglru (gated diagonal linear recurrence block),
-  polynorm_ff, moe_ff (softmax router with correction, neighbour groups, identity experts, shared expert).
+  add, optional silu gate before or after), dyt (dynamic-tanh norm, optionally chained into the next one), depth_mix (weighted
+  sum over the outputs of all layers so far), linear (tcgen05 GEMM, or the CUDA-core / GEMV product for true 32-bit, decode
+  rows and odd shapes), latent_attention (low-rank shared latent cache, absorbed projections, sink softmax), softmax_attention
+  (key / value cache, grouped heads, partial rotary, score cap, window with kept first positions, distance penalty, sink,
+  output gate, borrowed cache), rglru (gated diagonal linear recurrence block), delta_rule and state_space (matrix state per
+  head), polynorm_ff, xielu_ff, moe_ff (softmax router with correction, neighbour groups, identity experts, shared expert).
 
 Precision: `f32=True` runs every product in true 32-bit.  Otherwise weights and product operands are bf16 with f32
 accumulation; the residual stream, norms, softmax, router, recurrence and everything entering it are f32 in both modes.
@@ -18,9 +21,10 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .codec import (F_A_F32, F_BIAS, F_F32, F_GELU, F_NOROUND, F_OUT_F32, F_RESID, F_SIGMOID, K_BDGEMM, K_COMMIT, K_EMBED, K_GEMM,
-                    K_GGEMM, K_GNORM, K_LATENT_ATTN, K_LRU_SCAN, K_MOE_COMBINE, K_MOE_SORT, K_POLYNORM, K_ROUTER, K_TCONV, Op, _Plan)
-from .config import LatentAttentionConfig, MoEFFConfig, RglruConfig
+from .codec import (F_A_F32, F_BIAS, F_F32, F_GATE_POST, F_GATE_PRE, F_GELU, F_NOROUND, F_OUT_F32, F_RESID, F_SIGMOID, F_SILU, K_BDGEMM,
+                    K_CACHE_ATTN, K_COMMIT, K_DEPTH_MIX, K_DYT, K_EMBED, K_GEMM, K_GGEMM, K_GNORM, K_LATENT_ATTN, K_LRU_SCAN,
+                    K_MOE_COMBINE, K_MOE_SORT, K_MSTATE_SCAN, K_POLYNORM, K_ROT_APPEND, K_ROUTER, K_TCONV, K_XIELU, Op, _Plan)
+from .config import DeltaRuleConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SoftmaxAttentionConfig, StateSpaceConfig
 from .seq_state import SlotState
 
 
@@ -68,11 +72,11 @@ class StepBuilder:
         return out
 
     def time_conv(self, x: torch.Tensor, w: torch.Tensor, state: str, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                  add_input: bool = False, col: int = 0, channels: Optional[int] = None):
-        """out = (x if add_input) + bias + causal conv over time of x's columns [col, col + channels); w f32 [channels, taps]."""
+                  add_input: bool = False, col: int = 0, channels: Optional[int] = None, silu: bool = False):
+        """out = act((x if add_input) + bias + causal conv over time of x's columns [col, col + channels)); w f32 [channels, taps]."""
         taps = w.shape[1]
         n = channels or w.shape[0]
-        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_RESID if add_input else 0)
+        flags = self._oflag(out) | (F_BIAS if bias is not None else 0) | (F_RESID if add_input else 0) | (F_SILU if silu else 0)
         kw = dict(M=self.M, N=n, taps=taps, A=_ptr(x, col), lda=x.shape[1], B=w, C=out, ldc=out.shape[1], flags=flags)
         if bias is not None:
             kw["bias"] = bias
@@ -84,10 +88,17 @@ class StepBuilder:
 
     def group_norm(self, x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, out: torch.Tensor, n: Optional[int] = None,
                    col: int = 0, residual: Optional[torch.Tensor] = None, out_bf16: Optional[torch.Tensor] = None,
-                   append_at_position: bool = False):
+                   append_at_position: bool = False, gate: Optional[torch.Tensor] = None, gate_col: int = 0, gate_first: bool = False,
+                   weight_period: int = 0):
+        """out = (residual +) rms_unit_per_group(x) * w.  `gate` (f32 rows, columns from gate_col): the row times silu(gate) before the
+        statistics (gate_first) or after the weights.  weight_period > 0: w has that many entries and repeats (a per-head norm)."""
         n = n or w.shape[0]
-        kw = dict(M=self.M, N=n, i0=groups, f0=eps, A=_ptr(x, col), lda=x.shape[1], scale=w, C=out, ldc=out.shape[1],
+        kw = dict(M=self.M, N=n, i0=groups, f0=eps, A=_ptr(x, col), lda=x.shape[1], scale=w, C=out, ldc=out.shape[1], i2=weight_period,
                   flags=self._oflag(out) | (F_RESID if residual is not None else 0))
+        if gate is not None:
+            kw["p1"], kw["i1"] = _ptr(gate, gate_col), gate.shape[1]
+            kw["flags"] |= F_GATE_PRE if gate_first else F_GATE_POST
+            self.plan.keep.append(gate)
         if residual is not None:
             kw["res"], kw["ldr"] = residual, residual.shape[1]
         if out_bf16 is not None:
@@ -170,6 +181,125 @@ class StepBuilder:
                  p0=self.slot.cur[state + ".s"], C2=self.slot.next[state + ".s"], C=sy, ldc=sy.shape[1], flags=self._oflag(sy),
                  ws=ws, ws_bytes=ws.numel() * 4)
         return self.linear(sy, w["o"], out)
+
+    # ---- dynamic-tanh norm, depth mix ---------------------------------------------------------------
+    def _chain(self, kw: dict, chain):
+        """chain = (norm, out): also write out = dyt(result; norm) — the norm that reads the finished stream next."""
+        if chain is not None:
+            nw, nout = chain
+            kw.update(norm_out=nout, norm_w=nw["wb"], norm_ld=nout.shape[1], norm_eps=nw["alpha"])
+            if nout.dtype == torch.float32:
+                kw["flags"] = kw.get("flags", 0) | F_F32
+
+    def dyt(self, x: torch.Tensor, nw: dict, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+            out_bf16: Optional[torch.Tensor] = None, chain=None, rows: Optional[int] = None):
+        """out = (residual +) tanh(alpha x) * w + b.  nw: alpha (float), w, b f32 [N], wb = cat(w, b)."""
+        n = nw["w"].shape[0]
+        kw = dict(M=rows or self.M, N=n, f0=nw["alpha"], A=x, lda=x.shape[1], scale=nw["w"], bias=nw["b"], C=out, ldc=out.shape[1],
+                  flags=self._oflag(out) | (F_RESID if residual is not None else 0))
+        if residual is not None:
+            kw["res"], kw["ldr"] = residual, residual.shape[1]
+        if out_bf16 is not None:
+            kw["C2"] = out_bf16
+        self._chain(kw, chain)
+        self._op(K_DYT, **kw)
+        return out
+
+    def depth_mix(self, hist: torch.Tensor, count: int, weights: torch.Tensor, out: torch.Tensor, chain=None):
+        """out f32 [M, N] = sum_(j < count) weights[j] * hist[j]; hist f32 [slices, M, N]."""
+        kw = dict(M=self.M, N=hist.shape[2], i0=count, K=hist.shape[1] * hist.shape[2], A=hist, lda=hist.shape[2], p0=weights, C=out,
+                  ldc=out.shape[1], flags=F_OUT_F32)
+        self._chain(kw, chain)
+        self._op(K_DEPTH_MIX, **kw)
+        return out
+
+    # ---- softmax attention over a key / value cache ---------------------------------------------------
+    def softmax_attention(self, h: torch.Tensor, c: SoftmaxAttentionConfig, w: dict, kcache: str, vcache: str, out: torch.Tensor):
+        """h [M, width] (product-operand dtype) -> out f32 [M, width].  w: wqkv [(H + 2G) dim.. (+ H gate rows), width] — queries, then
+        (unless the layer borrows a cache) keys and values, then the gate rows; bqkv f32 or None; freq f32 [rot_dims / 2] or None;
+        sink f32 [H] or None; r12 f32 [2H] or None; o [width, H * vdim]; o_b f32 or None.  kcache / vcache name the slot's
+        append states to write (own projections) and read."""
+        M, H, G, d, dv = self.M, c.heads, c.kv_heads, c.dim, c.vdim
+        own = c.kv_from is None
+        kcol = H * d
+        vcol = kcol + (G * d if own else 0)
+        gcol = vcol + (G * dv if own else 0)
+        proj = self.linear(h, w["wqkv"], self.buf("sa.proj", M, w["wqkv"].shape[0]), bias=w.get("bqkv"))
+        kc, vc = self.slot.cur[kcache], self.slot.cur[vcache]
+        cf32 = F_F32 if kc.dtype == torch.float32 else 0
+        if own or c.rot_dims > 0:
+            kw = dict(M=M, i0=H, i1=G if own else 0, i2=d, cin=dv, taps=c.rot_dims, K=kcol, a_rows=vcol, A=proj, lda=proj.shape[1],
+                      p0=self.slot.pos, flags=cf32)
+            if c.rot_dims > 0:
+                kw["B"] = w["freq"]
+            if own:
+                kw.update(C=kc, ldc=kc.shape[1], C2=vc, ldr=vc.shape[1])
+            self._op(K_ROT_APPEND, **kw)
+        # key-range splits: many query blocks need none; a few rows (decoding) spread their keys over up to 64 blocks
+        HG = H // G
+        QB = 1 if M == 1 else max(1, min(16, M, 16 // HG))
+        tiles = max(1, -(-self.slot.max_pos // 32))
+        blocks = -(-M // QB) * G
+        splits = min(64, tiles) if M <= 8 else (1 if blocks >= 74 else max(1, min(16, tiles, -(-296 // blocks))))
+        oa = self.buf("sa.o", M, H * dv, self.adt)
+        kw = dict(M=M, N=H * dv, i0=H, i1=G, i2=d, cin=dv, f0=c.scale, f1=c.softcap, K=c.window, a_rows=c.keep_first if c.window > 0 else 0,
+                  A=proj, lda=proj.shape[1], B=kc, ldr=kc.shape[1], p1=vc, taps=vc.shape[1], p0=self.slot.pos, m_begin=splits,
+                  C=oa, ldc=oa.shape[1], flags=cf32 | self._oflag(oa))
+        if w.get("sink") is not None:
+            kw["scale"] = w["sink"]
+        if w.get("r12") is not None:
+            kw["bias"] = w["r12"]
+        if c.gate:
+            kw["res"], kw["col_mod"] = _ptr(proj, gcol), proj.shape[1]
+        if splits > 1:
+            ws = self.buf("sa.ws", 1, M * H * splits * (dv + 2))
+            kw["ws"], kw["ws_bytes"] = ws, ws.numel() * 4
+        self._op(K_CACHE_ATTN, **kw)
+        return self.linear(oa, w["o"], out, bias=w.get("o_b"))
+
+    # ---- recurrences with a matrix state per head -----------------------------------------------------
+    def _mstate(self, mode: int, rows: torch.Tensor, raw: torch.Tensor, H: int, G: int, dk: int, dv: int, kcol: int, vcol: int,
+                decay_col: int, write_col: int, w: dict, state: str, y: torch.Tensor):
+        wcols = 2 * H + (2 * G * dk if mode == 0 else 0)
+        ws = self.buf("ms.ws", self.M, wcols)
+        kw = dict(M=self.M, N=H * dv, taps=mode, i0=H, i1=G, i2=dk, cin=dv, K=kcol, a_rows=vcol, A=rows, lda=rows.shape[1], res=raw,
+                  ldr=raw.shape[1], col_mod=decay_col, m_begin=write_col, scale=w["A_log"], bias=w["dt_bias"],
+                  p0=self.slot.cur[state], C2=self.slot.next[state], C=y, ldc=y.shape[1], ws=ws, ws_bytes=ws.numel() * 4, flags=F_OUT_F32)
+        if mode == 1 and w.get("D") is not None:
+            kw["B"] = w["D"]
+        self._op(K_MSTATE_SCAN, **kw)
+        return y
+
+    def delta_rule(self, h: torch.Tensor, c: DeltaRuleConfig, w: dict, state: str, eps: float, out: torch.Tensor):
+        """h [M, width] -> out f32 [M, width].  w: win [2 G dim + 2 H vdim + 2 H, width] (q | k | v | output gate | decay input |
+        write-strength input), conv f32 [2 G dim + H vdim, taps], A_log, dt_bias f32 [H], norm f32 [vdim], o [width, H vdim]."""
+        M, H, G, d, dv = self.M, c.heads, c.kv_heads, c.dim, c.vdim
+        nconv = 2 * G * d + H * dv
+        raw = self.linear(h, w["win"], self.buf("dr.raw", M, nconv + H * dv + 2 * H))
+        cv = self.time_conv(raw, w["conv"], state + ".conv", self.buf("dr.cv", M, nconv), channels=nconv, silu=True)
+        y = self._mstate(0, cv, raw, H, G, d, dv, G * d, 2 * G * d, nconv + H * dv, nconv + H * dv + H, w, state + ".s", self.buf("dr.y", M, H * dv))
+        yn = self.group_norm(y, w["norm"], H, eps, self.buf("dr.yn", M, H * dv, self.adt), n=H * dv, gate=raw, gate_col=nconv, weight_period=dv)
+        return self.linear(yn, w["o"], out)
+
+    def state_space(self, h: torch.Tensor, c: StateSpaceConfig, w: dict, state: str, eps: float, out: torch.Tensor):
+        """h [M, width] -> out f32 [M, width].  w: win [2 inner + 2 G N + H, width] (z | x | B | C | dt), conv f32 [inner + 2 G N, taps],
+        conv_b f32 or None, A_log, dt_bias, D f32 [H], norm f32 [inner], o [width, inner]."""
+        M, H, P, N, G = self.M, c.heads, c.vdim, c.state, c.groups
+        inner, nconv = H * P, H * P + 2 * G * N
+        raw = self.linear(h, w["win"], self.buf("ss.raw", M, inner + nconv + H))
+        cv = self.time_conv(raw, w["conv"], state + ".conv", self.buf("ss.cv", M, nconv), bias=w.get("conv_b"), col=inner, channels=nconv,
+                            silu=True)
+        y = self._mstate(1, cv, raw, H, G, N, P, inner, inner + G * N, inner + nconv, 0, w, state + ".s", self.buf("ss.y", M, inner))
+        yn = self.group_norm(y, w["norm"], c.norm_groups, eps, self.buf("ss.yn", M, inner, self.adt), gate=raw, gate_col=0, gate_first=True)
+        return self.linear(yn, w["o"], out)
+
+    def xielu_ff(self, x: torch.Tensor, w: dict, out: torch.Tensor):
+        """out f32 = W_down xielu(W_up x); w: up [ff, width], down [width, ff], act f32 [2]."""
+        ff = w["up"].shape[0]
+        z = self.linear(x, w["up"], self.buf("ff.z", self.M, ff))
+        za = self.buf("ff.za", self.M, ff, self.adt)
+        self._op(K_XIELU, M=self.M, N=ff, A=z, lda=ff, p0=w["act"], C=za, ldc=ff, flags=self._oflag(za))
+        return self.linear(za, w["down"], out)
 
     def polynorm_ff(self, x: torch.Tensor, w: dict, eps: float, out: torch.Tensor):
         """out f32 = W_down polynorm(W_up x); w: up [ff, width], down [width, ff], act f32 [4]."""
