@@ -110,6 +110,54 @@ def init_synthetic(cfg: RedodraConfig, seed: int = 0) -> Dict[str, torch.Tensor]
     return w
 
 
+class Packer:
+    """Checkpoint tensors -> the layouts the mechanisms of seq_ops.StepBuilder take.  `raw(name)` gives a CPU f32 tensor."""
+
+    def __init__(self, raw: Callable[[str], torch.Tensor], device, f32: bool):
+        self.raw, self.device, self.wdt = raw, torch.device(device), torch.float32 if f32 else torch.bfloat16
+
+    def W(self, t):   # product operand
+        return t.to(self.device, self.wdt).contiguous()
+
+    def F(self, t):   # always-f32 parameter
+        return t.to(self.device, torch.float32).contiguous()
+
+    def norm(self, name: str) -> dict:
+        w, b = self.raw(name), self.raw(name + ".b")
+        return {"alpha": float(self.raw(name + ".alpha")), "w": self.F(w), "b": self.F(b), "wb": self.F(torch.cat([w, b]))}
+
+    def attention(self, p: str, m: SoftmaxAttentionConfig) -> dict:
+        raw, W, F = self.raw, self.W, self.F
+        parts = [p + "q"] + ([p + "k", p + "v"] if m.kv_from is None else [])
+        rows = [raw(n) for n in parts] + ([raw(p + "g")] if m.gate else [])
+        d = {"wqkv": W(torch.cat(rows, 0)), "o": W(raw(p + "o")), "bqkv": None, "o_b": None, "freq": None, "sink": None, "r12": None}
+        if m.bias:
+            d["bqkv"] = F(torch.cat([raw(n + ".b") for n in parts] + ([torch.zeros(m.heads)] if m.gate else [])))
+            d["o_b"] = F(raw(p + "o.b"))
+        if m.rot_dims > 0:
+            i = torch.arange(m.rot_dims // 2, dtype=torch.float64)
+            d["freq"] = F(torch.as_tensor(m.rot_base, dtype=torch.float64) ** (-2.0 * i / m.rot_dims))
+        if m.sink:
+            d["sink"] = F(raw(p + "sink"))
+        if m.distance:
+            d["r12"] = F(torch.cat([raw(p + "r1"), raw(p + "r2")]))
+        return d
+
+    def delta_rule(self, q: str) -> dict:
+        raw, W, F = self.raw, self.W, self.F
+        return {"win": W(torch.cat([raw(q + n) for n in ("q", "k", "v", "g", "a", "b")], 0)),
+                "conv": F(torch.cat([raw(q + n + ".conv") for n in ("q", "k", "v")], 0)), "A_log": F(raw(q + "A_log")),
+                "dt_bias": F(raw(q + "dt_bias")), "norm": F(raw(q + "norm")), "o": W(raw(q + "o"))}
+
+    def state_space(self, r: str) -> dict:
+        raw, W, F = self.raw, self.W, self.F
+        return {"win": W(raw(r + "in")), "conv": F(raw(r + "conv")), "conv_b": F(raw(r + "conv.b")), "A_log": F(raw(r + "A_log")),
+                "dt_bias": F(raw(r + "dt_bias")), "D": F(raw(r + "D")), "norm": F(raw(r + "norm")), "o": W(raw(r + "o"))}
+
+    def xielu_ff(self, p: str) -> dict:
+        return {"up": self.W(self.raw(p + "up")), "down": self.W(self.raw(p + "down")), "act": self.F(self.raw(p + "act"))}
+
+
 class RedodraModel:
     def __init__(self, cfg: RedodraConfig, get: Callable[[str], Optional[torch.Tensor]], device, f32: bool = False):
         """`get(name)` returns a CPU tensor or None."""
@@ -126,56 +174,25 @@ class RedodraModel:
                 raise ValueError(f"tensor {name!r} has shape {tuple(t.shape)}, the configuration implies {tuple(specs[name])}")
             return t.to(torch.float32)
 
-        def W(t):   # product operand
-            return t.to(self.device, self.wdt).contiguous()
-
-        def F(t):   # always-f32 parameter
-            return t.to(self.device, torch.float32).contiguous()
-
-        def norm(name):
-            w, b = raw(name), raw(name + ".b")
-            return {"alpha": float(raw(name + ".alpha")), "w": F(w), "b": F(b), "wb": F(torch.cat([w, b]))}
-
-        def attention(p, m: SoftmaxAttentionConfig):
-            parts = [p + "q"] + ([p + "k", p + "v"] if m.kv_from is None else [])
-            rows = [raw(n) for n in parts] + ([raw(p + "g")] if m.gate else [])
-            d = {"wqkv": W(torch.cat(rows, 0)), "o": W(raw(p + "o")), "bqkv": None, "o_b": None, "freq": None, "sink": None, "r12": None}
-            if m.bias:
-                d["bqkv"] = F(torch.cat([raw(n + ".b") for n in parts] + ([torch.zeros(m.heads)] if m.gate else [])))
-                d["o_b"] = F(raw(p + "o.b"))
-            if m.rot_dims > 0:
-                i = torch.arange(m.rot_dims // 2, dtype=torch.float64)
-                d["freq"] = F(torch.as_tensor(m.rot_base, dtype=torch.float64) ** (-2.0 * i / m.rot_dims))
-            if m.sink:
-                d["sink"] = F(raw(p + "sink"))
-            if m.distance:
-                d["r12"] = F(torch.cat([raw(p + "r1"), raw(p + "r2")]))
-            return d
-
-        self.g: Dict[str, object] = {"embed": W(raw("embed")), "final.norm": norm("final.norm"), "head": W(raw("head"))}
+        pk = Packer(raw, self.device, self.f32)
+        self.g: Dict[str, object] = {"embed": pk.W(raw("embed")), "final.norm": pk.norm("final.norm"), "head": pk.W(raw("head"))}
         self.layers: List[dict] = []
         for i, L in enumerate(cfg.layers):
             p = f"l{i}."
-            d: dict = {"norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b"), "dwa": F(raw(p + "dwa"))}
+            d: dict = {"norm1": pk.norm(p + "norm1"), "norm1b": pk.norm(p + "norm1b"), "dwa": pk.F(raw(p + "dwa"))}
             m = L.mixer
             q = p + "mix."
             if isinstance(m, DeltaRuleConfig):
-                d["mix"] = {"win": W(torch.cat([raw(q + n) for n in ("q", "k", "v", "g", "a", "b")], 0)),
-                            "conv": F(torch.cat([raw(q + n + ".conv") for n in ("q", "k", "v")], 0)), "A_log": F(raw(q + "A_log")),
-                            "dt_bias": F(raw(q + "dt_bias")), "norm": F(raw(q + "norm")), "o": W(raw(q + "o"))}
+                d["mix"] = pk.delta_rule(q)
             elif isinstance(m, SoftmaxAttentionConfig):
-                d["mix"] = attention(q, m)
+                d["mix"] = pk.attention(q, m)
             else:
-                r = q + "right."
-                d["mix"] = {"left": attention(q + "left.", m.left),
-                            "right": {"win": W(raw(r + "in")), "conv": F(raw(r + "conv")), "conv_b": F(raw(r + "conv.b")),
-                                      "A_log": F(raw(r + "A_log")), "dt_bias": F(raw(r + "dt_bias")), "D": F(raw(r + "D")),
-                                      "norm": F(raw(r + "norm")), "o": W(raw(r + "o"))},
-                            # the halving of the sum is folded into the two output norms' weights (exact: a power of two)
-                            "left_out": F(0.5 * raw(q + "left.out")), "right_out": F(0.5 * raw(q + "right.out"))}
+                # the halving of the sum is folded into the two output norms' weights (exact: a power of two)
+                d["mix"] = {"left": pk.attention(q + "left.", m.left), "right": pk.state_space(q + "right."),
+                            "left_out": pk.F(0.5 * raw(q + "left.out")), "right_out": pk.F(0.5 * raw(q + "right.out"))}
             if L.mlp is not None:
-                d["norm2"], d["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
-                d["ff"] = {"up": W(raw(p + "mlp.up")), "down": W(raw(p + "mlp.down")), "act": F(raw(p + "mlp.act"))}
+                d["norm2"], d["norm2b"] = pk.norm(p + "norm2"), pk.norm(p + "norm2b")
+                d["ff"] = pk.xielu_ff(p + "mlp.")
             self.layers.append(d)
 
     # ---- what a sequence keeps between steps ------------------------------------------------------
