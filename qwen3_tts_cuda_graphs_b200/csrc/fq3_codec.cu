@@ -1206,6 +1206,29 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       const int splits = std::max(1, o.m_begin), HG = o.i0 / o.i1;
       if (splits > 64) return fail("cache_attn: at most 64 key splits");
       if (splits > 1 && (!o.ws || o.ws_bytes < (int64_t)o.M * o.i0 * splits * (o.cin + 2) * 4)) return fail("cache_attn: workspace too small for the splits");
+      // bf16 cache and a prompt portion: the tensor-core kernel (FQ3S_ATTN_MMA=0: CUDA cores everywhere)
+      static int use_mma = -1;
+      if (use_mma < 0) { const char* e7 = getenv("FQ3S_ATTN_MMA"); use_mma = (e7 == nullptr || atoi(e7) != 0) ? 1 : 0; }
+      if (use_mma && !(o.flags & FQ3C_F32) && o.M > 8 && (HG == 1 || HG == 2 || HG == 4 || HG == 8 || HG == 16) && o.i2 % 16 == 0 && o.i2 <= 256 &&
+          o.cin % 16 == 0 && o.cin <= 128 && o.ldr % 8 == 0 && o.taps % 8 == 0 && !(reinterpret_cast<uintptr_t>(o.B) & 15) &&
+          !(reinterpret_cast<uintptr_t>(o.p1) & 15) && (o.ldc % 2 == 0 || (o.flags & FQ3C_OUT_F32))) {
+        static bool mattr[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !mattr[dev]) {
+          cudaFuncSetAttribute(fq3s_cache_attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          cudaFuncSetAttribute(fq3s_cache_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          cudaFuncSetAttribute(fq3s_cache_attn_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+          mattr[dev] = true;
+        }
+        const int QBLK = 64 / HG;
+        dim3 grid((o.M + QBLK - 1) / QBLK, o.i1);
+        const size_t smem = cache_attn_mma_smem(o.i2, o.cin);
+        if (o.cin <= 32) fq3s_cache_attn_mma_kernel<4><<<grid, 128, smem, s>>>(o);
+        else if (o.cin <= 64) fq3s_cache_attn_mma_kernel<8><<<grid, 128, smem, s>>>(o);
+        else fq3s_cache_attn_mma_kernel<16><<<grid, 128, smem, s>>>(o);
+        return 0;
+      }
       int QB = o.M == 1 ? 1 : std::max(1, std::min(std::min(16, o.M), 16 / HG)), TJ = 32;
       while (cache_attn_smem(QB * HG, TJ, o.i2, o.cin) > 200 * 1024 && QB > 1) QB >>= 1;
       while (cache_attn_smem(QB * HG, TJ, o.i2, o.cin) > 200 * 1024 && TJ > 4) TJ >>= 1;
@@ -1237,7 +1260,14 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
       count_launches(1);
       dim3 grid((o.cin + 31) / 32, o.i0);
-      const size_t smem = sizeof(float) * ((size_t)MS_CH * 2 * o.i2 + MS_CH * 32 + MS_CH * 2);
+      const size_t smem = mstate_scan_smem(o.i2);
+      static bool sattr[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !sattr[dev]) {
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        sattr[dev] = true;
+      }
       if (o.i2 <= 32) fq3s_mstate_scan_kernel<8><<<grid, 128, smem, s>>>(o);
       else if (o.i2 <= 64) fq3s_mstate_scan_kernel<16><<<grid, 128, smem, s>>>(o);
       else if (o.i2 <= 128) fq3s_mstate_scan_kernel<32><<<grid, 128, smem, s>>>(o);

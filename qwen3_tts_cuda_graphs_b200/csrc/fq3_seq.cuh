@@ -1396,6 +1396,215 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_merge_kernel(const fq3c_o
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores for bf16 caches and many queries (prompt portions).  The rows of an MMA tile are
+// (query, head of the group) pairs: a block takes 64 / HG consecutive queries x the HG query heads of one key / value head = 64
+// rows, 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
+// buffers (one is read while the next arrives); tiles outside every window of the block and beyond the kept first positions are
+// never fetched.  S [16 x 64] = Q K^T (m16n8k16, keys row-major as the B operand), then scale / cap / distance penalty / mask and
+// the online softmax in f32, then O [16 x dv] += P V with every weight as a bf16 pair p_hi + p_lo (two MMAs: 16 mantissa bits)
+// and the value tile through ldmatrix.trans.  Queries are rounded to bf16 once, as a bf16 product rounds its operand.
+// grid (ceil(M / (64 / HG)), key heads), 128 threads; the last queries (most keys) start first.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int CM_TJ = 64;
+__host__ __device__ inline size_t cache_attn_mma_smem(int d, int dv) { return 2 * ((size_t)64 * (d + 8) + 2 * (size_t)CM_TJ * (d + 8) + 2 * (size_t)CM_TJ * (dv + 8)); }
+template <int NTM>
+__global__ void __launch_bounds__(128) fq3s_cache_attn_mma_kernel(const fq3c_op o) {
+  extern __shared__ __align__(16) unsigned char cm_raw[];
+  const int H = o.i0, G = o.i1, d = o.i2, dv = o.cin, HG = H / G, QBLK = 64 / HG, LDK = d + 8, LDV = dv + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(cm_raw);            // [64][LDK]
+  bf16* Kt0 = Qs + (size_t)64 * LDK;                     // 2 x [CM_TJ][LDK]
+  bf16* Vt0 = Kt0 + (size_t)2 * CM_TJ * LDK;             // 2 x [CM_TJ][LDV]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * QBLK, kvh = blockIdx.y;
+  const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
+  const int nq = min(QBLK, o.M - m0), ifirst = P + m0, ilast = ifirst + nq - 1;
+  const int W = o.K, keep = o.a_rows;
+  const float* A = reinterpret_cast<const float*>(o.A);
+  for (int i = tid; i < 64 * d; i += 128) {
+    const int r = i / d, c = i - r * d, qi = r / HG, hh = r - qi * HG;
+    Qs[(size_t)r * LDK + c] = __float2bfloat16_rn(qi < nq ? A[(size_t)(m0 + qi) * o.lda + (size_t)(kvh * HG + hh) * d + c] : 0.f);
+  }
+  // the two rows this thread holds of its warp's 16
+  int qpos[2], head[2];
+  bool live[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int r = warp * 16 + g + e * 8, qi = r / HG;
+    live[e] = qi < nq;
+    qpos[e] = ifirst + qi;
+    head[e] = kvh * HG + (r - qi * HG);
+  }
+  const bool wactive = (warp * 16) / HG < nq;
+  const int wlast = ifirst + min(nq - 1, (warp * 16 + 15) / HG);
+  const int ntiles = ilast / CM_TJ + 1;
+  const int tkeep = W > 0 ? (keep + CM_TJ - 1) / CM_TJ : 0, tlo = W > 0 ? max(0, ifirst - W + 1) / CM_TJ : 0;
+  auto next_tile = [&](int tt) { ++tt; if (W > 0 && tt >= tkeep && tt < tlo) tt = tlo; return tt; };
+  const bf16* kc = reinterpret_cast<const bf16*>(o.B) + (size_t)kvh * d;
+  const bf16* vc = reinterpret_cast<const bf16*>(o.p1) + (size_t)kvh * dv;
+  const int kch = d >> 3, vch = dv >> 3;
+  auto fetch_tile = [&](const int tt, const int buf) {       // rows beyond the last needed position arrive as zeros
+    bf16* kd = Kt0 + (size_t)buf * CM_TJ * LDK;
+    bf16* vd = Vt0 + (size_t)buf * CM_TJ * LDV;
+    const int j0 = tt * CM_TJ;
+    for (int i = tid; i < CM_TJ * kch; i += 128) {
+      const int row = i / kch, c = i - row * kch;
+      const bool ok = j0 + row <= ilast;
+      cp_async16(kd + (size_t)row * LDK + c * 8, kc + (size_t)(ok ? j0 + row : 0) * o.ldr + c * 8, ok);
+    }
+    for (int i = tid; i < CM_TJ * vch; i += 128) {
+      const int row = i / vch, c = i - row * vch;
+      const bool ok = j0 + row <= ilast;
+      cp_async16(vd + (size_t)row * LDV + c * 8, vc + (size_t)(ok ? j0 + row : 0) * o.taps + c * 8, ok);
+    }
+    cp_async_commit();
+  };
+  float oacc[NTM][4];
+#pragma unroll
+  for (int i = 0; i < NTM; ++i) { oacc[i][0] = 0.f; oacc[i][1] = 0.f; oacc[i][2] = 0.f; oacc[i][3] = 0.f; }
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  const int nt_o = dv >> 3;
+  const float* r12 = reinterpret_cast<const float*>(o.bias);
+  const float cap = o.f1, icap = o.f1 > 0.f ? 1.f / o.f1 : 0.f;
+  float r1v[2] = {0.f, 0.f}, r2v[2] = {0.f, 0.f};
+  if (r12) { r1v[0] = r12[head[0]]; r1v[1] = r12[head[1]]; r2v[0] = r12[H + head[0]]; r2v[1] = r12[H + head[1]]; }
+  const bf16* Qw = Qs + (size_t)warp * 16 * LDK;
+  int tcur = next_tile(-1);
+  if (tcur < ntiles) fetch_tile(tcur, 0);
+  for (int it = 0; tcur < ntiles; ++it) {
+    const int tn = next_tile(tcur);
+    if (tn < ntiles) {
+      fetch_tile(tn, (it + 1) & 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int jt = tcur * CM_TJ;
+    const bf16* Kt = Kt0 + (size_t)(it & 1) * CM_TJ * LDK;
+    const bf16* Vt = Vt0 + (size_t)(it & 1) * CM_TJ * LDV;
+    if (wactive && jt <= wlast) {
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+      {
+        const int mi = lane >> 3, l7 = lane & 7;
+        const bf16* qa = Qw + (size_t)((mi & 1) * 8 + l7) * LDK + (mi >> 1) * 8;
+        const bf16* cb = Kt + (size_t)((mi >> 1) * 8 + l7) * LDK + (mi & 1) * 8;
+        for (int kk = 0; kk < d; kk += 16) {
+          uint32_t a[4];
+          ldmatrix_x4(a, qa + kk);
+#pragma unroll
+          for (int nt = 0; nt < 8; nt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, cb + (size_t)nt * 8 * LDK + kk);
+            mma16816(s[nt], a, b[0], b[1]);
+            mma16816(s[nt + 1], a, b[2], b[3]);
+          }
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = jt + nt * 8 + t * 2 + (e & 1), hf = e >> 1, i = qpos[hf];
+          float v = -INFINITY;
+          if (live[hf] && key <= i && (W <= 0 || i - key < W || key < keep)) {
+            v = s[nt][e] * o.f0;
+            if (cap > 0.f) v = cap * tanhf(v * icap);
+            if (r12) v -= r1v[hf] * log1pf(r2v[hf] * (float)(i - key));
+          }
+          s[nt][e] = v;
+          mx[hf] = fmaxf(mx[hf], v);
+        }
+      }
+      float al[2], u[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+        const float mn = fmaxf(mrow[hf], mx[hf]);
+        u[hf] = mn == -INFINITY ? 0.f : mn;
+        al[hf] = mrow[hf] == -INFINITY ? 0.f : expf(mrow[hf] - u[hf]);
+        mrow[hf] = mn;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        s[nt][0] = expf(s[nt][0] - u[0]); s[nt][1] = expf(s[nt][1] - u[0]);
+        s[nt][2] = expf(s[nt][2] - u[1]); s[nt][3] = expf(s[nt][3] - u[1]);
+        sum[0] += s[nt][0] + s[nt][1];
+        sum[1] += s[nt][2] + s[nt][3];
+      }
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        sum[hf] += __shfl_xor_sync(0xffffffffu, sum[hf], 1);
+        sum[hf] += __shfl_xor_sync(0xffffffffu, sum[hf], 2);
+        lrow[hf] = lrow[hf] * al[hf] + sum[hf];
+      }
+#pragma unroll
+      for (int nt = 0; nt < NTM; ++nt) { oacc[nt][0] *= al[0]; oacc[nt][1] *= al[0]; oacc[nt][2] *= al[1]; oacc[nt][3] *= al[1]; }
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t ah[4], alo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float p0 = s[2 * ks + (q >> 1)][(q & 1) * 2], p1 = s[2 * ks + (q >> 1)][(q & 1) * 2 + 1];
+          const float h0f = bf16r(p0), h1f = bf16r(p1);
+          ah[q] = pack_bf16(h0f, h1f);
+          alo[q] = pack_bf16(p0 - h0f, p1 - h1f);
+        }
+        const int mi = lane >> 3;
+        const bf16* base = Vt + (size_t)(ks * 16 + (mi & 1) * 8 + (lane & 7)) * LDV + (mi >> 1) * 8;
+#pragma unroll
+        for (int nt0 = 0; nt0 < NTM; nt0 += 8) {
+          uint32_t b[4][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (nt0 + 2 * q < nt_o) ldmatrix_x4_trans(b[q], base + (nt0 + 2 * q) * 8);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int nt = nt0 + 2 * q;
+            if (nt < nt_o) mma16816(oacc[nt], ah, b[q][0], b[q][1]);
+            if (nt + 1 < nt_o) mma16816(oacc[nt + 1], ah, b[q][2], b[q][3]);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int nt = nt0 + 2 * q;
+            if (nt < nt_o) mma16816(oacc[nt], alo, b[q][0], b[q][1]);
+            if (nt + 1 < nt_o) mma16816(oacc[nt + 1], alo, b[q][2], b[q][3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    tcur = tn;
+  }
+  const float* sink = reinterpret_cast<const float*>(o.scale);
+  const float* gate = reinterpret_cast<const float*>(o.res);
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    if (!live[hf]) continue;
+    const int h = head[hf], m = qpos[hf] - P;
+    float f = 1.f, den = lrow[hf];
+    if (sink) {
+      const float mm = fmaxf(mrow[hf], sink[h]);
+      f = mrow[hf] == -INFINITY ? 0.f : expf(mrow[hf] - mm);
+      den = den * f + expf(sink[h] - mm);
+    }
+    float sc = f / den;
+    if (gate) sc *= sigmoid_f(gate[(size_t)m * o.col_mod + h]);
+    const size_t at = (size_t)m * o.ldc + (size_t)h * dv;
+#pragma unroll
+    for (int nt = 0; nt < NTM; ++nt) {
+      if (nt >= nt_o) continue;
+      const float v0 = oacc[nt][hf * 2] * sc, v1 = oacc[nt][hf * 2 + 1] * sc;
+      if (o.flags & FQ3C_OUT_F32) { reinterpret_cast<float*>(o.C)[at + nt * 8 + t * 2] = v0; reinterpret_cast<float*>(o.C)[at + nt * 8 + t * 2 + 1] = v1; }
+      else *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<bf16*>(o.C) + at + nt * 8 + t * 2) = __floats2bfloat162_rn(v0, v1);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
 // Recurrences with a matrix state S [dk, dv] per head.  Two launches: the per-token coefficients (and, for the delta rule, the unit
 // query / key vectors) are computed row-parallel into ws; then one block per (head, 32 state columns) walks the tokens in order.
 // A state column is held by four lanes (dk / 4 entries each, interleaved), so a token costs each lane dk / 4 multiply-adds per
@@ -1435,7 +1644,12 @@ __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) 
 }
 
 constexpr int MS_CH = 16;     // tokens staged per round
-// grid (ceil(dv / 32), H), 128 threads: thread = (column tid / 4 of the tile, lane-of-four tid % 4)
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__host__ __device__ inline size_t mstate_scan_smem(int dk) { return sizeof(float) * 2 * ((size_t)MS_CH * 2 * dk + MS_CH * 32 + MS_CH * 2); }
+// grid (ceil(dv / 32), H), 128 threads: thread = (column tid / 4 of the tile, lane-of-four tid % 4).  The next round's tokens
+// arrive by cp.async while the current round is walked.
 template <int RPT>
 __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) {
   extern __shared__ float msm[];
@@ -1444,9 +1658,7 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const int wc = mstate_ws_cols(H, G, dk, delta);
   const int tid = threadIdx.x, sub = tid & 3, col = blockIdx.x * 32 + (tid >> 2);
   const bool live = col < dv;
-  float* kq = msm;                              // [MS_CH][2][dk]: (k, q) or (B, C)
-  float* vs = kq + (size_t)MS_CH * 2 * dk;      // [MS_CH][32]
-  float* cf = vs + MS_CH * 32;                  // [MS_CH][2]
+  const int per = MS_CH * 2 * dk + MS_CH * 32 + MS_CH * 2;      // floats per buffer: (k, q) or (B, C) [MS_CH][2][dk] | v [MS_CH][32] | coefficients [MS_CH][2]
   float S[RPT];
   const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
 #pragma unroll
@@ -1455,59 +1667,78 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const float* wsb = reinterpret_cast<const float*>(o.ws);
   const float* rows = reinterpret_cast<const float*>(o.A);
   const int vcol = (delta ? o.a_rows : 0) + h * dv;
-  for (int t0 = 0; t0 < o.M; t0 += MS_CH) {
+  auto fetch = [&](const int t0, float* buf) {
     const int nt = min(MS_CH, o.M - t0);
-    __syncthreads();
-    for (int idx = tid; idx < nt * 2 * dk; idx += blockDim.x) {
-      const int tt = idx / (2 * dk), e = idx - tt * 2 * dk, which = e / dk, c = e - which * dk;
-      float v;
-      if (delta) v = wsb[(size_t)(t0 + tt) * wc + 2 * H + (size_t)((which == 0 ? G : 0) + g) * dk + c];      // k first, then q
-      else v = rows[(size_t)(t0 + tt) * o.lda + (which == 0 ? o.K : o.a_rows) + (size_t)g * dk + c];           // B first, then C
-      kq[idx] = v;
+    float* kq = buf;
+    float* vs = kq + (size_t)MS_CH * 2 * dk;
+    float* cf = vs + MS_CH * 32;
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* src0 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)(G + g) * dk : rows + (size_t)(t0 + tt) * o.lda + o.K + (size_t)g * dk;
+      const float* src1 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)g * dk : rows + (size_t)(t0 + tt) * o.lda + o.a_rows + (size_t)g * dk;
+      for (int c = tid; c < dk; c += 128) {
+        cp_async4(kq + (size_t)tt * 2 * dk + c, src0 + c);
+        cp_async4(kq + (size_t)tt * 2 * dk + dk + c, src1 + c);
+      }
     }
-    for (int idx = tid; idx < nt * 32; idx += blockDim.x) {
+    for (int idx = tid; idx < nt * 32; idx += 128) {
       const int tt = idx >> 5, c = blockIdx.x * 32 + (idx & 31);
-      vs[idx] = c < dv ? rows[(size_t)(t0 + tt) * o.lda + vcol + c] : 0.f;
+      if (c < dv) cp_async4(vs + idx, rows + (size_t)(t0 + tt) * o.lda + vcol + c);
+      else vs[idx] = 0.f;
     }
-    for (int idx = tid; idx < nt * 2; idx += blockDim.x) {
-      const int tt = idx >> 1, which = idx & 1;
-      cf[idx] = wsb[(size_t)(t0 + tt) * wc + which * H + h];
+    for (int idx = tid; idx < nt * 2; idx += 128) cp_async4(cf + idx, wsb + (size_t)(t0 + (idx >> 1)) * wc + (idx & 1) * H + h);
+    cp_async_commit();
+  };
+  fetch(0, msm);
+  int it = 0;
+  for (int t0 = 0; t0 < o.M; t0 += MS_CH, ++it) {
+    const int nt = min(MS_CH, o.M - t0);
+    if (t0 + MS_CH < o.M) {
+      fetch(t0 + MS_CH, msm + (size_t)((it + 1) & 1) * per);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    const float* kq = msm + (size_t)(it & 1) * per;
+    const float* vs = kq + (size_t)MS_CH * 2 * dk;
+    const float* cf = vs + MS_CH * 32;
     for (int tt = 0; tt < nt; ++tt) {
       const float* kk = kq + (size_t)tt * 2 * dk;
       const float* qq = kk + dk;
       const float c1 = cf[tt * 2], c2 = cf[tt * 2 + 1], v = vs[tt * 32 + (tid >> 2)];
-      float os = 0.f;
+      float os[4] = {0.f, 0.f, 0.f, 0.f};       // four chains, so that a product's sum is not one long dependent row of multiply-adds
       if (delta) {
-        float ks = 0.f;
+        float ks[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < RPT; ++r) {
           const int i = r * 4 + sub;
           S[r] *= c1;
-          if (i < dk) ks = fmaf(kk[i], S[r], ks);
+          if (i < dk) ks[r & 3] = fmaf(kk[i], S[r], ks[r & 3]);
         }
-        ks += __shfl_xor_sync(0xffffffffu, ks, 1);
-        ks += __shfl_xor_sync(0xffffffffu, ks, 2);
-        const float u = c2 * (v - ks);
+        float kt = (ks[0] + ks[1]) + (ks[2] + ks[3]);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 1);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 2);
+        const float u = c2 * (v - kt);
 #pragma unroll
         for (int r = 0; r < RPT; ++r) {
           const int i = r * 4 + sub;
-          if (i < dk) { S[r] = fmaf(kk[i], u, S[r]); os = fmaf(qq[i], S[r], os); }
+          if (i < dk) { S[r] = fmaf(kk[i], u, S[r]); os[r & 3] = fmaf(qq[i], S[r], os[r & 3]); }
         }
       } else {
         const float dx = c2 * v;
 #pragma unroll
         for (int r = 0; r < RPT; ++r) {
           const int i = r * 4 + sub;
-          if (i < dk) { S[r] = fmaf(c1, S[r], kk[i] * dx); os = fmaf(qq[i], S[r], os); }
+          if (i < dk) { S[r] = fmaf(c1, S[r], kk[i] * dx); os[r & 3] = fmaf(qq[i], S[r], os[r & 3]); }
         }
       }
-      os += __shfl_xor_sync(0xffffffffu, os, 1);
-      os += __shfl_xor_sync(0xffffffffu, os, 2);
-      if (!delta) os = fmaf(D, v, os);
-      if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = os;
+      float ot = (os[0] + os[1]) + (os[2] + os[3]);
+      ot += __shfl_xor_sync(0xffffffffu, ot, 1);
+      ot += __shfl_xor_sync(0xffffffffu, ot, 2);
+      if (!delta) ot = fmaf(D, v, ot);
+      if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = ot;
     }
+    __syncthreads();
   }
   float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * dk * dv;
 #pragma unroll

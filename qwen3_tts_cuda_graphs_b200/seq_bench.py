@@ -1,6 +1,7 @@
 """Throughput of a sequence model at layer sizes that resemble a real model's, beside the closest model of the framework.
 
-`bench.py --seq-model` (the default workload of bench.py is untouched).  Random weights, synthetic tokens.  For each size:
+`bench.py --seq-model` (the default workload of bench.py is untouched).  Random weights, synthetic tokens.  Sizes w* are Sidalorn
+models, r* Redodra models (`--seq-sizes r1024,w1024` puts the two designs side by side at equal width).  For each size:
   * prefill: one step of T prompt tokens through `SequenceEngine.step` (tokens / s), and the same in portions;
   * decode: single-token steps at context T (tokens / s), replayed as CUDA graphs as the generation path does;
   * per op kind: device time of every op of the step's list launched alone (CUDA events, L2 flushed before each timed
@@ -20,12 +21,15 @@ from collections import defaultdict
 import torch
 
 from . import codec as K
-from .config import (DenseFFConfig, LatentAttentionConfig, MoEFFConfig, RglruConfig, SeqLayerConfig, SidalornConfig)
+from .config import (DeltaRuleConfig, DenseFFConfig, LatentAttentionConfig, MoEFFConfig, ParallelMixerConfig, RedodraConfig, RglruConfig,
+                     SeqLayerConfig, SidalornConfig, SoftmaxAttentionConfig, StateSpaceConfig)
 
 KIND_NAMES = {K.K_GEMM: "gemm (tcgen05 / gemv)", K.K_RMSNORM: "rmsnorm", K.K_ATTN: "attention (prefill, CUDA cores)", 8: "qk-norm + rope + kv",
               K.K_EMBED: "embed / gather", K.K_TCONV: "time conv", K.K_GNORM: "group norm", K.K_BDGEMM: "block-diagonal product",
               K.K_LATENT_ATTN: "latent attention", K.K_LRU_SCAN: "lru scan", K.K_POLYNORM: "polynorm", K.K_ROUTER: "router",
-              K.K_MOE_SORT: "moe sort", K.K_GGEMM: "grouped expert product", K.K_MOE_COMBINE: "moe combine", K.K_COMMIT: "state commit"}
+              K.K_MOE_SORT: "moe sort", K.K_GGEMM: "grouped expert product", K.K_MOE_COMBINE: "moe combine", K.K_COMMIT: "state commit",
+              K.K_DYT: "dynamic-tanh norm", K.K_DEPTH_MIX: "depth mix", K.K_XIELU: "xielu", K.K_ROT_APPEND: "rotary + cache append",
+              K.K_CACHE_ATTN: "cached softmax attention", K.K_MSTATE_SCAN: "matrix-state scan"}
 
 
 def peaks():
@@ -49,10 +53,31 @@ def sizes():
                        SeqLayerConfig("latent_attention", att, moe)]
         return SidalornConfig(vocab, width, 1e-5, 4, 3, tuple(layers))
 
-    return {"w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1)}
+    def redodra(width, heads, kv, window, ssm_heads, ssm_vdim, ff, order, vocab=3072):
+        att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, 30.0, 64, 50000.0, sink=True, gate=True)
+        left = SoftmaxAttentionConfig(heads // 2, max(1, kv // 2), 128, 128, 128 ** -0.5, 30.0, window=window, keep_first=4, bias=True, distance=True)
+        mix = {"delta": DeltaRuleConfig(heads // 2, heads // 4, 128, 128, 4), "attention": att,
+               "parallel": ParallelMixerConfig(left, StateSpaceConfig(ssm_heads, ssm_vdim, 128, 2, 4, 2))}
+        layers, lender = [], None
+        for t in order:
+            if t == "shared":
+                layers.append(SeqLayerConfig("attention", SoftmaxAttentionConfig(**dict(att.__dict__, kv_from=lender)), DenseFFConfig(ff)))
+                continue
+            if t == "attention":
+                lender = len(layers)
+            layers.append(SeqLayerConfig(t, mix[t], DenseFFConfig(ff)))
+        return RedodraConfig(vocab, width, 1e-5, tuple(layers))
+
+    return {"w1024": model(1024, 16, 256, 8, 3072, 14, 2, 768, 1536), "w2048": model(2048, 16, 512, 16, 6144, 30, 4, 1024, 2048, pairs=1),
+            "r1024": redodra(1024, 16, 4, 512, 16, 64, 3072, ("delta", "attention", "parallel", "shared", "delta", "parallel")),
+            "r2048": redodra(2048, 32, 8, 1024, 32, 64, 6144, ("delta", "attention", "parallel"))}
 
 
-def random_model(cfg: SidalornConfig, device, seed=0):
+def random_model(cfg, device, seed=0):
+    if isinstance(cfg, RedodraConfig):
+        from .redodra import RedodraModel, init_synthetic
+
+        return RedodraModel(cfg, init_synthetic(cfg, seed).get, device, f32=False)
     from .sidalorn import SidalornModel, tensor_specs
 
     g = torch.Generator(device=device).manual_seed(seed)
@@ -90,6 +115,16 @@ def op_cost(o, ctx_keys: float):
         return 4.0 * M * o.i0 * o.i2 * ctx_keys, M * (o.i0 + 2 * o.i1) * o.i2 * 2 + M * o.i0 * o.i2 * 2
     if k == K.K_LRU_SCAN:
         return 0.0, M * N * (4 * 4 + outs)
+    if k == K.K_CACHE_ATTN:
+        keys = min(ctx_keys, o.K + o.a_rows) if o.K > 0 else ctx_keys
+        return 2.0 * M * o.i0 * (o.i2 + o.cin) * keys, min(ctx_keys + M / 2, keys + M) * o.i1 * (o.i2 + o.cin) * ws + M * o.i0 * (o.i2 * 4 + o.cin * outs)
+    if k == K.K_MSTATE_SCAN:
+        per = 7.0 if o.taps == 0 else 5.0
+        return per * M * o.i0 * o.i2 * o.cin, M * (2 * o.i1 * o.i2 + 2 * o.i0 * o.cin) * 4 + 2 * o.i0 * o.i2 * o.cin * 4
+    if k == K.K_ROT_APPEND:
+        return 0.0, M * (o.i0 * o.i2 * 8 + o.i1 * (o.i2 + o.cin) * (4 + ws))
+    if k == K.K_DEPTH_MIX:
+        return 0.0, M * N * 4 * (o.i0 + 1)
     if k == K.K_COMMIT:
         return 0.0, 0.0
     if k in (K.K_ROUTER, K.K_MOE_SORT):
@@ -152,7 +187,7 @@ def timed(fn, warmup=3, reps=5, flush=None):
     return sorted(ts)[len(ts) // 2]
 
 
-def bench_sidalorn(name, cfg, T, device):
+def bench_sequence_model(name, cfg, T, device):
     from .seq_engine import SequenceEngine
 
     model = random_model(cfg, device)
@@ -160,7 +195,7 @@ def bench_sidalorn(name, cfg, T, device):
     g = torch.Generator().manual_seed(1)
     toks = torch.randint(0, cfg.vocab, (T + 40,), generator=g).tolist()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-    out = {"model": f"Sidalorn {name}", "width": cfg.width, "layers": len(cfg.layers), "T": T}
+    out = {"model": f"{cfg.architecture} {name}", "width": cfg.width, "layers": len(cfg.layers), "T": T}
 
     def prefill(portion):
         def run():
@@ -186,8 +221,16 @@ def bench_sidalorn(name, cfg, T, device):
     ms = timed(decode, flush=flush)
     out["decode_ms_per_token"], out["decode_tok_s"] = round(ms / 32, 4), round(32 / ms * 1e3)
     # weights a decode step streams: everything but the unchosen experts and the embedding table's other rows
+    def operand_bytes(v):
+        if isinstance(v, dict):
+            return sum(operand_bytes(x) for x in v.values())
+        return v.numel() * v.element_size() if isinstance(v, torch.Tensor) and v.dtype == torch.bfloat16 else 0
+
     wb = 0
     for i, (L, w) in enumerate(zip(cfg.layers, model.layers)):
+        if isinstance(cfg, RedodraConfig):
+            wb += operand_bytes(w)
+            continue
         for k, t in w["mix"].items():
             wb += t.numel() * t.element_size() if t is not None else 0
         f = w.get("ff")
@@ -252,7 +295,7 @@ def main(T: int = 2048, which: str = "w1024,w2048"):
     res = {"bench": "sequence model beside the closest existing model", "data": "synthetic", "dtype": "bf16", "rows": []}
     all_sizes = sizes()
     for name in which.split(","):
-        res["rows"].append(bench_sidalorn(name, all_sizes[name], T, device))
+        res["rows"].append(bench_sequence_model(name, all_sizes[name], T, device))
         torch.cuda.empty_cache()
     res["rows"].append(bench_talker(T, device))
     print(json.dumps(res))
