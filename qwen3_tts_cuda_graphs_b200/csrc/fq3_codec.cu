@@ -1221,12 +1221,12 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
           cudaFuncSetAttribute(fq3s_cache_attn_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
           mattr[dev] = true;
         }
-        const int QBLK = 64 / HG;
+        const int ROWS = (o.M * HG >= 8192 && cache_attn_mma_smem(128, o.i2, o.cin) <= 110 * 1024) ? 128 : 64, QBLK = ROWS / HG;
         dim3 grid((o.M + QBLK - 1) / QBLK, o.i1);
-        const size_t smem = cache_attn_mma_smem(o.i2, o.cin);
-        if (o.cin <= 32) fq3s_cache_attn_mma_kernel<4><<<grid, 128, smem, s>>>(o);
-        else if (o.cin <= 64) fq3s_cache_attn_mma_kernel<8><<<grid, 128, smem, s>>>(o);
-        else fq3s_cache_attn_mma_kernel<16><<<grid, 128, smem, s>>>(o);
+        const size_t smem = cache_attn_mma_smem(ROWS, o.i2, o.cin);
+        if (o.cin <= 32) fq3s_cache_attn_mma_kernel<4><<<grid, ROWS * 2, smem, s>>>(o, ROWS);
+        else if (o.cin <= 64) fq3s_cache_attn_mma_kernel<8><<<grid, ROWS * 2, smem, s>>>(o, ROWS);
+        else fq3s_cache_attn_mma_kernel<16><<<grid, ROWS * 2, smem, s>>>(o, ROWS);
         return 0;
       }
       int QB = o.M == 1 ? 1 : std::max(1, std::min(std::min(16, o.M), 16 / HG)), TJ = 32;
@@ -1259,19 +1259,18 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       if (o.i2 > 256) return fail("mstate_scan: at most 256 state rows per head");
       fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
       count_launches(1);
-      dim3 grid((o.cin + 31) / 32, o.i0);
-      const size_t smem = mstate_scan_smem(o.i2);
+      dim3 grid((o.cin + MS_COLS - 1) / MS_COLS, o.i0);
       static bool sattr[64] = {};
       int dev = 0;
       cudaGetDevice(&dev);
       if (dev >= 0 && dev < 64 && !sattr[dev]) {
-        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         sattr[dev] = true;
       }
-      if (o.i2 <= 32) fq3s_mstate_scan_kernel<8><<<grid, 128, smem, s>>>(o);
-      else if (o.i2 <= 64) fq3s_mstate_scan_kernel<16><<<grid, 128, smem, s>>>(o);
-      else if (o.i2 <= 128) fq3s_mstate_scan_kernel<32><<<grid, 128, smem, s>>>(o);
-      else fq3s_mstate_scan_kernel<64><<<grid, 128, smem, s>>>(o);
+      if (o.i2 <= 32) fq3s_mstate_scan_kernel<4><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4), s>>>(o);
+      else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8), s>>>(o);
+      else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16), s>>>(o);
+      else fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o);
       return 0;
     }
     default: return 1;

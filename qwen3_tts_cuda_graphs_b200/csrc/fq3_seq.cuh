@@ -1398,29 +1398,29 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_merge_kernel(const fq3c_o
 // ---------------------------------------------------------------------------------------------------------------------------
 // The same attention on the tensor cores for bf16 caches and many queries (prompt portions).  The rows of an MMA tile are
 // (query, head of the group) pairs: a block takes 64 / HG consecutive queries x the HG query heads of one key / value head = 64
-// rows, 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
+// rows (128 for long portions), 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
 // buffers (one is read while the next arrives); tiles outside every window of the block and beyond the kept first positions are
 // never fetched.  S [16 x 64] = Q K^T (m16n8k16, keys row-major as the B operand), then scale / cap / distance penalty / mask and
 // the online softmax in f32, then O [16 x dv] += P V with every weight as a bf16 pair p_hi + p_lo (two MMAs: 16 mantissa bits)
 // and the value tile through ldmatrix.trans.  Queries are rounded to bf16 once, as a bf16 product rounds its operand.
-// grid (ceil(M / (64 / HG)), key heads), 128 threads; the last queries (most keys) start first.
+// grid (ceil(M / (rows / HG)), key heads), 2 threads per row; the last queries (most keys) start first.
 // ---------------------------------------------------------------------------------------------------------------------------
 constexpr int CM_TJ = 64;
-__host__ __device__ inline size_t cache_attn_mma_smem(int d, int dv) { return 2 * ((size_t)64 * (d + 8) + 2 * (size_t)CM_TJ * (d + 8) + 2 * (size_t)CM_TJ * (dv + 8)); }
+__host__ __device__ inline size_t cache_attn_mma_smem(int rows, int d, int dv) { return 2 * ((size_t)rows * (d + 8) + 2 * (size_t)CM_TJ * (d + 8) + 2 * (size_t)CM_TJ * (dv + 8)); }
 template <int NTM>
-__global__ void __launch_bounds__(128) fq3s_cache_attn_mma_kernel(const fq3c_op o) {
+__global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op o, const int ROWS) {
   extern __shared__ __align__(16) unsigned char cm_raw[];
-  const int H = o.i0, G = o.i1, d = o.i2, dv = o.cin, HG = H / G, QBLK = 64 / HG, LDK = d + 8, LDV = dv + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(cm_raw);            // [64][LDK]
-  bf16* Kt0 = Qs + (size_t)64 * LDK;                     // 2 x [CM_TJ][LDK]
+  const int H = o.i0, G = o.i1, d = o.i2, dv = o.cin, HG = H / G, QBLK = ROWS / HG, LDK = d + 8, LDV = dv + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(cm_raw);            // [ROWS][LDK]
+  bf16* Kt0 = Qs + (size_t)ROWS * LDK;                     // 2 x [CM_TJ][LDK]
   bf16* Vt0 = Kt0 + (size_t)2 * CM_TJ * LDK;             // 2 x [CM_TJ][LDV]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int tid = threadIdx.x, nth = blockDim.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int m0 = (gridDim.x - 1 - blockIdx.x) * QBLK, kvh = blockIdx.y;
   const int P = o.p0 ? *reinterpret_cast<const int*>(o.p0) : 0;
   const int nq = min(QBLK, o.M - m0), ifirst = P + m0, ilast = ifirst + nq - 1;
   const int W = o.K, keep = o.a_rows;
   const float* A = reinterpret_cast<const float*>(o.A);
-  for (int i = tid; i < 64 * d; i += 128) {
+  for (int i = tid; i < ROWS * d; i += nth) {
     const int r = i / d, c = i - r * d, qi = r / HG, hh = r - qi * HG;
     Qs[(size_t)r * LDK + c] = __float2bfloat16_rn(qi < nq ? A[(size_t)(m0 + qi) * o.lda + (size_t)(kvh * HG + hh) * d + c] : 0.f);
   }
@@ -1446,12 +1446,12 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_mma_kernel(const fq3c_op 
     bf16* kd = Kt0 + (size_t)buf * CM_TJ * LDK;
     bf16* vd = Vt0 + (size_t)buf * CM_TJ * LDV;
     const int j0 = tt * CM_TJ;
-    for (int i = tid; i < CM_TJ * kch; i += 128) {
+    for (int i = tid; i < CM_TJ * kch; i += nth) {
       const int row = i / kch, c = i - row * kch;
       const bool ok = j0 + row <= ilast;
       cp_async16(kd + (size_t)row * LDK + c * 8, kc + (size_t)(ok ? j0 + row : 0) * o.ldr + c * 8, ok);
     }
-    for (int i = tid; i < CM_TJ * vch; i += 128) {
+    for (int i = tid; i < CM_TJ * vch; i += nth) {
       const int row = i / vch, c = i - row * vch;
       const bool ok = j0 + row <= ilast;
       cp_async16(vd + (size_t)row * LDV + c * 8, vc + (size_t)(ok ? j0 + row : 0) * o.taps + c * 8, ok);
@@ -1606,9 +1606,9 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_mma_kernel(const fq3c_op 
 
 // ---------------------------------------------------------------------------------------------------------------------------
 // Recurrences with a matrix state S [dk, dv] per head.  Two launches: the per-token coefficients (and, for the delta rule, the unit
-// query / key vectors) are computed row-parallel into ws; then one block per (head, 32 state columns) walks the tokens in order.
-// A state column is held by four lanes (dk / 4 entries each, interleaved), so a token costs each lane dk / 4 multiply-adds per
-// product plus two shuffles per reduction; tokens arrive in chunks staged through shared memory.
+// query / key vectors) are computed row-parallel into ws; then one block per (head, 16 state columns) walks the tokens in order.
+// A state column is held by eight lanes (dk / 8 consecutive entries each), so a token costs each lane dk / 8 multiply-adds per
+// product plus three shuffles per reduction; tokens arrive in rounds staged through shared memory.
 // ws row m: [c1[H] | c2[H] | unit q [G * dk] | unit k [G * dk]]  (delta rule: c1 = decay, c2 = write strength; scan: c1 = decay, c2 = dt)
 // ---------------------------------------------------------------------------------------------------------------------------
 __host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) { return 2 * H + (delta ? 2 * G * dk : 0); }
@@ -1644,46 +1644,53 @@ __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) 
 }
 
 constexpr int MS_CH = 16;     // tokens staged per round
+constexpr int MS_COLS = 16;   // state columns per block (eight lanes each)
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-__host__ __device__ inline size_t mstate_scan_smem(int dk) { return sizeof(float) * 2 * ((size_t)MS_CH * 2 * dk + MS_CH * 32 + MS_CH * 2); }
-// grid (ceil(dv / 32), H), 128 threads: thread = (column tid / 4 of the tile, lane-of-four tid % 4).  The next round's tokens
-// arrive by cp.async while the current round is walked.
+// floats per staging buffer: (k, q) or (B, C) [MS_CH][2][8 slices of RPT + 4] | v [MS_CH][MS_COLS] | coefficients [MS_CH][2]
+__host__ __device__ constexpr int mstate_buf_floats(int rpt) { return MS_CH * 2 * 8 * (rpt + 4) + MS_CH * MS_COLS + MS_CH * 2; }
+// grid (ceil(dv / 16), H), 128 threads: thread = (column tid / 8 of the tile, lane-of-eight tid % 8).  A lane holds RPT consecutive
+// rows of its state column (RPT * 8 >= dk; rows beyond dk stay zero: their key / query entries are zero padding), reads its slice
+// of the token's key and query with 16-byte shared-memory loads (slices are padded apart by four floats: no bank conflicts),
+// and a product is finished by three shuffles.  The next round's tokens arrive by cp.async while the current round is walked.
 template <int RPT>
 __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) {
-  extern __shared__ float msm[];
+  extern __shared__ __align__(16) float msm[];
+  constexpr int SL = RPT + 4, ROW = 8 * SL;
   const int H = o.i0, G = o.i1, dk = o.i2, dv = o.cin, h = blockIdx.y, g = h / (H / G);
   const bool delta = o.taps == 0;
   const int wc = mstate_ws_cols(H, G, dk, delta);
-  const int tid = threadIdx.x, sub = tid & 3, col = blockIdx.x * 32 + (tid >> 2);
+  const int tid = threadIdx.x, sub = tid & 7, cl = tid >> 3, col = blockIdx.x * MS_COLS + cl;
   const bool live = col < dv;
-  const int per = MS_CH * 2 * dk + MS_CH * 32 + MS_CH * 2;      // floats per buffer: (k, q) or (B, C) [MS_CH][2][dk] | v [MS_CH][32] | coefficients [MS_CH][2]
+  constexpr int per = mstate_buf_floats(RPT);
+  for (int i = tid; i < 2 * per; i += 128) msm[i] = 0.f;        // the padding stays zero for the whole launch
   float S[RPT];
   const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) { const int i = r * 4 + sub; S[r] = (live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
+  for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; S[r] = (live && i < dk) ? st[(size_t)i * dv + col] : 0.f; }
   const float D = (!delta && o.B) ? reinterpret_cast<const float*>(o.B)[h] : 0.f;
   const float* wsb = reinterpret_cast<const float*>(o.ws);
   const float* rows = reinterpret_cast<const float*>(o.A);
   const int vcol = (delta ? o.a_rows : 0) + h * dv;
+  __syncthreads();
   auto fetch = [&](const int t0, float* buf) {
     const int nt = min(MS_CH, o.M - t0);
     float* kq = buf;
-    float* vs = kq + (size_t)MS_CH * 2 * dk;
-    float* cf = vs + MS_CH * 32;
+    float* vs = kq + MS_CH * 2 * ROW;
+    float* cf = vs + MS_CH * MS_COLS;
     for (int tt = 0; tt < nt; ++tt) {
       const float* src0 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)(G + g) * dk : rows + (size_t)(t0 + tt) * o.lda + o.K + (size_t)g * dk;
       const float* src1 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)g * dk : rows + (size_t)(t0 + tt) * o.lda + o.a_rows + (size_t)g * dk;
       for (int c = tid; c < dk; c += 128) {
-        cp_async4(kq + (size_t)tt * 2 * dk + c, src0 + c);
-        cp_async4(kq + (size_t)tt * 2 * dk + dk + c, src1 + c);
+        const int at = (c / RPT) * SL + (c % RPT);
+        cp_async4(kq + tt * 2 * ROW + at, src0 + c);
+        cp_async4(kq + tt * 2 * ROW + ROW + at, src1 + c);
       }
     }
-    for (int idx = tid; idx < nt * 32; idx += 128) {
-      const int tt = idx >> 5, c = blockIdx.x * 32 + (idx & 31);
+    for (int idx = tid; idx < nt * MS_COLS; idx += 128) {
+      const int tt = idx / MS_COLS, c = blockIdx.x * MS_COLS + (idx % MS_COLS);
       if (c < dv) cp_async4(vs + idx, rows + (size_t)(t0 + tt) * o.lda + vcol + c);
-      else vs[idx] = 0.f;
     }
     for (int idx = tid; idx < nt * 2; idx += 128) cp_async4(cf + idx, wsb + (size_t)(t0 + (idx >> 1)) * wc + (idx & 1) * H + h);
     cp_async_commit();
@@ -1693,48 +1700,57 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   for (int t0 = 0; t0 < o.M; t0 += MS_CH, ++it) {
     const int nt = min(MS_CH, o.M - t0);
     if (t0 + MS_CH < o.M) {
-      fetch(t0 + MS_CH, msm + (size_t)((it + 1) & 1) * per);
+      fetch(t0 + MS_CH, msm + ((it + 1) & 1) * per);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const float* kq = msm + (size_t)(it & 1) * per;
-    const float* vs = kq + (size_t)MS_CH * 2 * dk;
-    const float* cf = vs + MS_CH * 32;
+    const float* kq = msm + (it & 1) * per;
+    const float* vs = kq + MS_CH * 2 * ROW;
+    const float* cf = vs + MS_CH * MS_COLS;
     for (int tt = 0; tt < nt; ++tt) {
-      const float* kk = kq + (size_t)tt * 2 * dk;
-      const float* qq = kk + dk;
-      const float c1 = cf[tt * 2], c2 = cf[tt * 2 + 1], v = vs[tt * 32 + (tid >> 2)];
+      const float4* k4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + sub * SL);
+      const float4* q4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + ROW + sub * SL);
+      const float c1 = cf[tt * 2], c2 = cf[tt * 2 + 1], v = vs[tt * MS_COLS + cl];
       float os[4] = {0.f, 0.f, 0.f, 0.f};       // four chains, so that a product's sum is not one long dependent row of multiply-adds
       if (delta) {
         float ks[4] = {0.f, 0.f, 0.f, 0.f};
+        float4 kv[RPT / 4];
 #pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-          const int i = r * 4 + sub;
-          S[r] *= c1;
-          if (i < dk) ks[r & 3] = fmaf(kk[i], S[r], ks[r & 3]);
+        for (int r = 0; r < RPT / 4; ++r) {
+          kv[r] = k4[r];
+          ks[0] = fmaf(kv[r].x, S[4 * r], ks[0]); ks[1] = fmaf(kv[r].y, S[4 * r + 1], ks[1]);
+          ks[2] = fmaf(kv[r].z, S[4 * r + 2], ks[2]); ks[3] = fmaf(kv[r].w, S[4 * r + 3], ks[3]);
         }
         float kt = (ks[0] + ks[1]) + (ks[2] + ks[3]);
         kt += __shfl_xor_sync(0xffffffffu, kt, 1);
         kt += __shfl_xor_sync(0xffffffffu, kt, 2);
-        const float u = c2 * (v - kt);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 4);
+        const float u = c2 * (v - c1 * kt);      // S^T k of the decayed state = decay * (S^T k of the stored one)
 #pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-          const int i = r * 4 + sub;
-          if (i < dk) { S[r] = fmaf(kk[i], u, S[r]); os[r & 3] = fmaf(qq[i], S[r], os[r & 3]); }
+        for (int r = 0; r < RPT / 4; ++r) {
+          const float4 qv = q4[r];
+          S[4 * r] = fmaf(kv[r].x, u, c1 * S[4 * r]); S[4 * r + 1] = fmaf(kv[r].y, u, c1 * S[4 * r + 1]);
+          S[4 * r + 2] = fmaf(kv[r].z, u, c1 * S[4 * r + 2]); S[4 * r + 3] = fmaf(kv[r].w, u, c1 * S[4 * r + 3]);
+          os[0] = fmaf(qv.x, S[4 * r], os[0]); os[1] = fmaf(qv.y, S[4 * r + 1], os[1]);
+          os[2] = fmaf(qv.z, S[4 * r + 2], os[2]); os[3] = fmaf(qv.w, S[4 * r + 3], os[3]);
         }
       } else {
         const float dx = c2 * v;
 #pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-          const int i = r * 4 + sub;
-          if (i < dk) { S[r] = fmaf(c1, S[r], kk[i] * dx); os[r & 3] = fmaf(qq[i], S[r], os[r & 3]); }
+        for (int r = 0; r < RPT / 4; ++r) {
+          const float4 bv = k4[r], qv = q4[r];
+          S[4 * r] = fmaf(c1, S[4 * r], bv.x * dx); S[4 * r + 1] = fmaf(c1, S[4 * r + 1], bv.y * dx);
+          S[4 * r + 2] = fmaf(c1, S[4 * r + 2], bv.z * dx); S[4 * r + 3] = fmaf(c1, S[4 * r + 3], bv.w * dx);
+          os[0] = fmaf(qv.x, S[4 * r], os[0]); os[1] = fmaf(qv.y, S[4 * r + 1], os[1]);
+          os[2] = fmaf(qv.z, S[4 * r + 2], os[2]); os[3] = fmaf(qv.w, S[4 * r + 3], os[3]);
         }
       }
       float ot = (os[0] + os[1]) + (os[2] + os[3]);
       ot += __shfl_xor_sync(0xffffffffu, ot, 1);
       ot += __shfl_xor_sync(0xffffffffu, ot, 2);
+      ot += __shfl_xor_sync(0xffffffffu, ot, 4);
       if (!delta) ot = fmaf(D, v, ot);
       if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = ot;
     }
@@ -1742,5 +1758,5 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   }
   float* nst = reinterpret_cast<float*>(o.C2) + (size_t)h * dk * dv;
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) { const int i = r * 4 + sub; if (live && i < dk) nst[(size_t)i * dv + col] = S[r]; }
+  for (int r = 0; r < RPT; ++r) { const int i = sub * RPT + r; if (live && i < dk) nst[(size_t)i * dv + col] = S[r]; }
 }
