@@ -124,7 +124,7 @@ enum fq3c_kind {
                              g = exp(-exp(A_log) softplus(a + dt_bias));  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
                            scan: dt = softplus(dt + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  o = S^T C + D x
                          State read from p0 (f32 [i0, i2, cin]), next state written to C2 (FQ3C_COMMIT installs it); C f32 [M, i0 * cin];
-                         ws = f32 [M, 2 * i0 + (taps == 0 ? 2 * i1 * i2 : 0)] for the per-token coefficients (and unit vectors)       */
+                         ws = f32 [M, round_up(2 * i0 + (taps == 0 ? 2 * i1 * i2 + i1 : 0), 4)]: unit vectors, coefficients, q.k       */
 };
 
 enum fq3c_flags {

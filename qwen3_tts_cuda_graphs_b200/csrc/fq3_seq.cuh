@@ -1248,6 +1248,41 @@ struct CacheAttnMask {
   int window, keep;
   __device__ __forceinline__ bool sees(int i, int j) const { return j <= i && (window <= 0 || i - j < window || j < keep); }
 };
+// rows [0, nvalid) of a cache tile into shared memory as f32 (the rest of the nrows as zeros): 16-byte loads, several in flight,
+// where the rows allow them
+__device__ __forceinline__ void ca_unpack(float* d, const uint4& u, const float*) {
+  d[0] = __uint_as_float(u.x); d[1] = __uint_as_float(u.y); d[2] = __uint_as_float(u.z); d[3] = __uint_as_float(u.w);
+}
+__device__ __forceinline__ void ca_unpack(float* d, const uint4& u, const bf16*) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { d[2 * i] = __uint_as_float(w[i] << 16); d[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <typename TC>
+__device__ __forceinline__ void ca_stage_rows(float* dst, const int dld, const TC* src, const int sld, const int nvalid, const int nrows,
+                                              const int cols, const int tid, const int nth) {
+  constexpr int V = 16 / (int)sizeof(TC);
+  if (cols % V == 0 && sld % V == 0 && !(reinterpret_cast<uintptr_t>(src) & 15)) {
+    const int cpr = cols / V;
+#pragma unroll 4
+    for (int idx = tid; idx < nrows * cpr; idx += nth) {
+      const int jj = idx / cpr, c = (idx - jj * cpr) * V;
+      float* d = dst + (size_t)jj * dld + c;
+      if (jj < nvalid) {
+        const uint4 u = *reinterpret_cast<const uint4*>(src + (size_t)jj * sld + c);
+        ca_unpack(d, u, src);
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) d[i] = 0.f;
+      }
+    }
+    return;
+  }
+  for (int idx = tid; idx < nrows * cols; idx += nth) {
+    const int jj = idx / cols, c = idx - jj * cols;
+    dst[(size_t)jj * dld + c] = jj < nvalid ? ldf<TC>(src + (size_t)jj * sld + c) : 0.f;
+  }
+}
 template <typename TC>
 __global__ void __launch_bounds__(256) fq3s_cache_attn_kernel(const fq3c_op o, const int QB, const int TJ, const int splits) {
   extern __shared__ float csm[];
@@ -1284,14 +1319,8 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_kernel(const fq3c_op o, c
     // nothing of this tile is inside the widest window of the block (that of its first query) nor among the kept positions
     if (mask.window > 0 && j0 + jn <= ifirst - mask.window + 1 && j0 >= mask.keep) continue;
     __syncthreads();
-    for (int idx = tid; idx < TJ * d; idx += blockDim.x) {
-      const int jj = idx / d, c = idx - jj * d;
-      kt[(size_t)jj * (d + 1) + c] = jj < jn ? ldf<TC>(kc + (size_t)(j0 + jj) * o.ldr + c) : 0.f;
-    }
-    for (int idx = tid; idx < TJ * dv; idx += blockDim.x) {
-      const int jj = idx / dv, c = idx - jj * dv;
-      vt[idx] = jj < jn ? ldf<TC>(vc + (size_t)(j0 + jj) * o.taps + c) : 0.f;
-    }
+    ca_stage_rows<TC>(kt, d + 1, kc + (size_t)j0 * o.ldr, o.ldr, jn, TJ, d, tid, blockDim.x);
+    ca_stage_rows<TC>(vt, dv, vc + (size_t)j0 * o.taps, o.taps, jn, TJ, dv, tid, blockDim.x);
     __syncthreads();
     for (int idx = tid; idx < R * TJ; idx += blockDim.x) {
       const int r = idx / TJ, jj = idx - r * TJ, qi = r / HG, i = ifirst + qi, j = j0 + jj;
@@ -1401,11 +1430,17 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_merge_kernel(const fq3c_o
 // rows (128 for long portions), 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
 // buffers (one is read while the next arrives); tiles outside every window of the block and beyond the kept first positions are
 // never fetched.  S [16 x 64] = Q K^T (m16n8k16, keys row-major as the B operand), then scale / cap / distance penalty / mask and
-// the online softmax in f32, then O [16 x dv] += P V with every weight as a bf16 pair p_hi + p_lo (two MMAs: 16 mantissa bits)
+// the online softmax in f32 (fast exponential, logarithm and reciprocal: errors around 1e-6), then O [16 x dv] += P V with every weight as a bf16 pair p_hi + p_lo (two MMAs: 16 mantissa bits)
 // and the value tile through ldmatrix.trans.  Queries are rounded to bf16 once, as a bf16 product rounds its operand.
 // grid (ceil(M / (rows / HG)), key heads), 2 threads per row; the last queries (most keys) start first.
 // ---------------------------------------------------------------------------------------------------------------------------
 constexpr int CM_TJ = 64;
+// tanh through one fast exponential and one fast reciprocal (relative error around 1e-6: far below the bf16 operands' rounding,
+// which is the precision this kernel serves; the 32-bit mode runs the CUDA-core kernel with the full-precision functions)
+__device__ __forceinline__ float fast_tanh(float x) {
+  const float e = __expf(2.f * fminf(fmaxf(x, -15.f), 15.f));
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
 __host__ __device__ inline size_t cache_attn_mma_smem(int rows, int d, int dv) { return 2 * ((size_t)rows * (d + 8) + 2 * (size_t)CM_TJ * (d + 8) + 2 * (size_t)CM_TJ * (dv + 8)); }
 template <int NTM>
 __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op o, const int ROWS) {
@@ -1420,9 +1455,22 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
   const int nq = min(QBLK, o.M - m0), ifirst = P + m0, ilast = ifirst + nq - 1;
   const int W = o.K, keep = o.a_rows;
   const float* A = reinterpret_cast<const float*>(o.A);
-  for (int i = tid; i < ROWS * d; i += nth) {
-    const int r = i / d, c = i - r * d, qi = r / HG, hh = r - qi * HG;
-    Qs[(size_t)r * LDK + c] = __float2bfloat16_rn(qi < nq ? A[(size_t)(m0 + qi) * o.lda + (size_t)(kvh * HG + hh) * d + c] : 0.f);
+  if (o.lda % 4 == 0 && !(reinterpret_cast<uintptr_t>(A) & 15)) {      // 16-byte loads, four in flight per thread
+    const int c4 = d >> 2;
+#pragma unroll 4
+    for (int i = tid; i < ROWS * c4; i += nth) {
+      const int r = i / c4, c = (i - r * c4) * 4, qi = r / HG, hh = r - qi * HG;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (qi < nq) v = *reinterpret_cast<const float4*>(A + (size_t)(m0 + qi) * o.lda + (size_t)(kvh * HG + hh) * d + c);
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(Qs + (size_t)r * LDK + c);
+      dst[0] = __floats2bfloat162_rn(v.x, v.y);
+      dst[1] = __floats2bfloat162_rn(v.z, v.w);
+    }
+  } else {
+    for (int i = tid; i < ROWS * d; i += nth) {
+      const int r = i / d, c = i - r * d, qi = r / HG, hh = r - qi * HG;
+      Qs[(size_t)r * LDK + c] = __float2bfloat16_rn(qi < nq ? A[(size_t)(m0 + qi) * o.lda + (size_t)(kvh * HG + hh) * d + c] : 0.f);
+    }
   }
   // the two rows this thread holds of its warp's 16
   int qpos[2], head[2];
@@ -1435,7 +1483,7 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
     head[e] = kvh * HG + (r - qi * HG);
   }
   const bool wactive = (warp * 16) / HG < nq;
-  const int wlast = ifirst + min(nq - 1, (warp * 16 + 15) / HG);
+  const int wfirst = ifirst + (warp * 16) / HG, wlast = ifirst + min(nq - 1, (warp * 16 + 15) / HG);
   const int ntiles = ilast / CM_TJ + 1;
   const int tkeep = W > 0 ? (keep + CM_TJ - 1) / CM_TJ : 0, tlo = W > 0 ? max(0, ifirst - W + 1) / CM_TJ : 0;
   auto next_tile = [&](int tt) { ++tt; if (W > 0 && tt >= tkeep && tt < tlo) tt = tlo; return tt; };
@@ -1502,6 +1550,8 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
           }
         }
       }
+      // a tile every row of the warp sees whole needs no per-score test (most tiles of a long portion)
+      const bool whole = nq == QBLK && jt + CM_TJ - 1 <= wfirst && (W <= 0 || wlast - jt < W);
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
@@ -1509,10 +1559,10 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
         for (int e = 0; e < 4; ++e) {
           const int key = jt + nt * 8 + t * 2 + (e & 1), hf = e >> 1, i = qpos[hf];
           float v = -INFINITY;
-          if (live[hf] && key <= i && (W <= 0 || i - key < W || key < keep)) {
+          if (whole || (live[hf] && key <= i && (W <= 0 || i - key < W || key < keep))) {
             v = s[nt][e] * o.f0;
-            if (cap > 0.f) v = cap * tanhf(v * icap);
-            if (r12) v -= r1v[hf] * log1pf(r2v[hf] * (float)(i - key));
+            if (cap > 0.f) v = cap * fast_tanh(v * icap);
+            if (r12) v -= r1v[hf] * __logf(fmaf(r2v[hf], (float)(i - key), 1.f));
           }
           s[nt][e] = v;
           mx[hf] = fmaxf(mx[hf], v);
@@ -1530,8 +1580,8 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
       }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = expf(s[nt][0] - u[0]); s[nt][1] = expf(s[nt][1] - u[0]);
-        s[nt][2] = expf(s[nt][2] - u[1]); s[nt][3] = expf(s[nt][3] - u[1]);
+        s[nt][0] = __expf(s[nt][0] - u[0]); s[nt][1] = __expf(s[nt][1] - u[0]);
+        s[nt][2] = __expf(s[nt][2] - u[1]); s[nt][3] = __expf(s[nt][3] - u[1]);
         sum[0] += s[nt][0] + s[nt][1];
         sum[1] += s[nt][2] + s[nt][3];
       }
@@ -1609,22 +1659,25 @@ __global__ void __launch_bounds__(256) fq3s_cache_attn_mma_kernel(const fq3c_op 
 // query / key vectors) are computed row-parallel into ws; then one block per (head, 16 state columns) walks the tokens in order.
 // A state column is held by eight lanes (dk / 8 consecutive entries each), so a token costs each lane dk / 8 multiply-adds per
 // product plus three shuffles per reduction; tokens arrive in rounds staged through shared memory.
-// ws row m: [c1[H] | c2[H] | unit q [G * dk] | unit k [G * dk]]  (delta rule: c1 = decay, c2 = write strength; scan: c1 = decay, c2 = dt)
+// ws row m (padded to a multiple of four floats): [unit q [G * dk] | unit k [G * dk] |] c1[H] | c2[H] [| q.k [G]]  (bracketed parts: delta
+// rule only; delta rule: c1 = decay, c2 = write strength; scan: c1 = decay, c2 = dt)
 // ---------------------------------------------------------------------------------------------------------------------------
-__host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) { return 2 * H + (delta ? 2 * G * dk : 0); }
+__host__ __device__ inline int mstate_ws_cols(int H, int G, int dk, bool delta) { return ((delta ? 2 * G * dk + G : 0) + 2 * H + 3) & ~3; }
+__host__ __device__ inline int mstate_ws_coef(int G, int dk, bool delta) { return delta ? 2 * G * dk : 0; }      // column of c1
 
 // grid (M), 128 threads
 __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) {
   const int m = blockIdx.x, H = o.i0, G = o.i1, dk = o.i2;
   const bool delta = o.taps == 0;
   float* w = reinterpret_cast<float*>(o.ws) + (size_t)m * mstate_ws_cols(H, G, dk, delta);
+  float* cf = w + mstate_ws_coef(G, dk, delta);
   const float* raw = reinterpret_cast<const float*>(o.res) + (size_t)m * o.ldr;
   const float* alog = reinterpret_cast<const float*>(o.scale);
   const float* dtb = reinterpret_cast<const float*>(o.bias);
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float sp = softplus_f(raw[o.col_mod + h] + (dtb ? dtb[h] : 0.f));
-    w[h] = expf(-expf(alog[h]) * sp);
-    w[H + h] = delta ? sigmoid_f(raw[o.m_begin + h]) : sp;
+    cf[h] = expf(-expf(alog[h]) * sp);
+    cf[H + h] = delta ? sigmoid_f(raw[o.m_begin + h]) : sp;
   }
   if (!delta) return;
   const float* row = reinterpret_cast<const float*>(o.A) + (size_t)m * o.lda;
@@ -1638,8 +1691,17 @@ __global__ void __launch_bounds__(128) fq3s_mstate_prep_kernel(const fq3c_op o) 
     for (int c = lane; c < dk; c += 32) ss = fmaf(x[c], x[c], ss);
     ss = warp_sum(ss);
     const float f = (1.f / sqrtf(ss + 1e-6f)) * (isk ? 1.f : qs);
-    float* dst = w + 2 * H + (size_t)v * dk;
+    float* dst = w + (size_t)v * dk;
     for (int c = lane; c < dk; c += 32) dst[c] = x[c] * f;
+  }
+  __syncthreads();
+  for (int g = warp; g < G; g += nwarp) {          // q.k of the unit vectors: lets the scan read out through the state before the write
+    const float* qn = w + (size_t)g * dk;
+    const float* kn = qn + (size_t)G * dk;
+    float dot = 0.f;
+    for (int c = lane; c < dk; c += 32) dot = fmaf(qn[c], kn[c], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) cf[2 * H + g] = dot;
   }
 }
 
@@ -1648,8 +1710,8 @@ constexpr int MS_COLS = 16;   // state columns per block (eight lanes each)
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-// floats per staging buffer: (k, q) or (B, C) [MS_CH][2][8 slices of RPT + 4] | v [MS_CH][MS_COLS] | coefficients [MS_CH][2]
-__host__ __device__ constexpr int mstate_buf_floats(int rpt) { return MS_CH * 2 * 8 * (rpt + 4) + MS_CH * MS_COLS + MS_CH * 2; }
+// floats per staging buffer: (k, q) or (B, C) [MS_CH][2][8 slices of RPT + 4] | v [MS_CH][MS_COLS] | coefficients [MS_CH][4]
+__host__ __device__ constexpr int mstate_buf_floats(int rpt) { return MS_CH * 2 * 8 * (rpt + 4) + MS_CH * MS_COLS + MS_CH * 4; }
 // grid (ceil(dv / 16), H), 128 threads: thread = (column tid / 8 of the tile, lane-of-eight tid % 8).  A lane holds RPT consecutive
 // rows of its state column (RPT * 8 >= dk; rows beyond dk stay zero: their key / query entries are zero padding), reads its slice
 // of the token's key and query with 16-byte shared-memory loads (slices are padded apart by four floats: no bank conflicts),
@@ -1664,7 +1726,10 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const int tid = threadIdx.x, sub = tid & 7, cl = tid >> 3, col = blockIdx.x * MS_COLS + cl;
   const bool live = col < dv;
   constexpr int per = mstate_buf_floats(RPT);
-  for (int i = tid; i < 2 * per; i += 128) msm[i] = 0.f;        // the padding stays zero for the whole launch
+  {   // the padding between and behind the slices stays zero for the whole launch (only the token rows that will be used)
+    const int used = min(o.M, MS_CH) * 2 * ROW;
+    for (int i = tid; i < 2 * used; i += 128) msm[(i < used ? 0 : per - used) + i] = 0.f;
+  }
   float S[RPT];
   const float* st = reinterpret_cast<const float*>(o.p0) + (size_t)h * dk * dv;
 #pragma unroll
@@ -1674,25 +1739,44 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
   const float* rows = reinterpret_cast<const float*>(o.A);
   const int vcol = (delta ? o.a_rows : 0) + h * dv;
   __syncthreads();
+  // keys then queries (B then C) of this head's group, as columns of the rows they are staged from
+  const float* vsrc = delta ? wsb : rows;
+  const int vstride = delta ? wc : o.lda, off0 = (delta ? G * dk : o.K) + g * dk, off1 = (delta ? 0 : o.a_rows) + g * dk;
+  const int cfo = mstate_ws_coef(G, dk, delta);
+  const bool vec = dk % 4 == 0 && vstride % 4 == 0 && off0 % 4 == 0 && off1 % 4 == 0 && !(reinterpret_cast<uintptr_t>(vsrc) & 15);
   auto fetch = [&](const int t0, float* buf) {
     const int nt = min(MS_CH, o.M - t0);
     float* kq = buf;
     float* vs = kq + MS_CH * 2 * ROW;
     float* cf = vs + MS_CH * MS_COLS;
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* src0 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)(G + g) * dk : rows + (size_t)(t0 + tt) * o.lda + o.K + (size_t)g * dk;
-      const float* src1 = delta ? wsb + (size_t)(t0 + tt) * wc + 2 * H + (size_t)g * dk : rows + (size_t)(t0 + tt) * o.lda + o.a_rows + (size_t)g * dk;
-      for (int c = tid; c < dk; c += 128) {
-        const int at = (c / RPT) * SL + (c % RPT);
-        cp_async4(kq + tt * 2 * ROW + at, src0 + c);
-        cp_async4(kq + tt * 2 * ROW + ROW + at, src1 + c);
+    if (vec) {        // 16-byte copies: four consecutive entries never straddle a lane's slice (RPT is a multiple of four)
+      const int n4 = dk >> 2;
+      for (int idx = tid; idx < nt * n4; idx += 128) {
+        const int tt = idx / n4, c = (idx - tt * n4) * 4, at = (c / RPT) * SL + (c % RPT);
+        const float* sr = vsrc + (size_t)(t0 + tt) * vstride;
+        cp_async16(kq + tt * 2 * ROW + at, sr + off0 + c, true);
+        cp_async16(kq + tt * 2 * ROW + ROW + at, sr + off1 + c, true);
+      }
+    } else {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float* sr = vsrc + (size_t)(t0 + tt) * vstride;
+        for (int c = tid; c < dk; c += 128) {
+          const int at = (c / RPT) * SL + (c % RPT);
+          cp_async4(kq + tt * 2 * ROW + at, sr + off0 + c);
+          cp_async4(kq + tt * 2 * ROW + ROW + at, sr + off1 + c);
+        }
       }
     }
     for (int idx = tid; idx < nt * MS_COLS; idx += 128) {
       const int tt = idx / MS_COLS, c = blockIdx.x * MS_COLS + (idx % MS_COLS);
       if (c < dv) cp_async4(vs + idx, rows + (size_t)(t0 + tt) * o.lda + vcol + c);
     }
-    for (int idx = tid; idx < nt * 2; idx += 128) cp_async4(cf + idx, wsb + (size_t)(t0 + (idx >> 1)) * wc + (idx & 1) * H + h);
+    for (int idx = tid; idx < nt * 3; idx += 128) {
+      const int tt = idx / 3, which = idx - tt * 3;
+      const float* sr = wsb + (size_t)(t0 + tt) * wc + cfo;
+      if (which < 2) cp_async4(cf + tt * 4 + which, sr + which * H + h);
+      else if (delta) cp_async4(cf + tt * 4 + 2, sr + 2 * H + g);
+    }
     cp_async_commit();
   };
   fetch(0, msm);
@@ -1712,30 +1796,34 @@ __global__ void __launch_bounds__(128) fq3s_mstate_scan_kernel(const fq3c_op o) 
     for (int tt = 0; tt < nt; ++tt) {
       const float4* k4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + sub * SL);
       const float4* q4 = reinterpret_cast<const float4*>(kq + tt * 2 * ROW + ROW + sub * SL);
-      const float c1 = cf[tt * 2], c2 = cf[tt * 2 + 1], v = vs[tt * MS_COLS + cl];
+      const float c1 = cf[tt * 4], c2 = cf[tt * 4 + 1], v = vs[tt * MS_COLS + cl];
       float os[4] = {0.f, 0.f, 0.f, 0.f};       // four chains, so that a product's sum is not one long dependent row of multiply-adds
       if (delta) {
+        // both products with the stored state in one pass and one round of shuffles: with S' = c1 S + k u^T,
+        // S'^T q = c1 S^T q + u (k . q), and u = c2 (v - c1 S^T k); k . q comes with the token
         float ks[4] = {0.f, 0.f, 0.f, 0.f};
         float4 kv[RPT / 4];
 #pragma unroll
         for (int r = 0; r < RPT / 4; ++r) {
           kv[r] = k4[r];
+          const float4 qv = q4[r];
           ks[0] = fmaf(kv[r].x, S[4 * r], ks[0]); ks[1] = fmaf(kv[r].y, S[4 * r + 1], ks[1]);
           ks[2] = fmaf(kv[r].z, S[4 * r + 2], ks[2]); ks[3] = fmaf(kv[r].w, S[4 * r + 3], ks[3]);
-        }
-        float kt = (ks[0] + ks[1]) + (ks[2] + ks[3]);
-        kt += __shfl_xor_sync(0xffffffffu, kt, 1);
-        kt += __shfl_xor_sync(0xffffffffu, kt, 2);
-        kt += __shfl_xor_sync(0xffffffffu, kt, 4);
-        const float u = c2 * (v - c1 * kt);      // S^T k of the decayed state = decay * (S^T k of the stored one)
-#pragma unroll
-        for (int r = 0; r < RPT / 4; ++r) {
-          const float4 qv = q4[r];
-          S[4 * r] = fmaf(kv[r].x, u, c1 * S[4 * r]); S[4 * r + 1] = fmaf(kv[r].y, u, c1 * S[4 * r + 1]);
-          S[4 * r + 2] = fmaf(kv[r].z, u, c1 * S[4 * r + 2]); S[4 * r + 3] = fmaf(kv[r].w, u, c1 * S[4 * r + 3]);
           os[0] = fmaf(qv.x, S[4 * r], os[0]); os[1] = fmaf(qv.y, S[4 * r + 1], os[1]);
           os[2] = fmaf(qv.z, S[4 * r + 2], os[2]); os[3] = fmaf(qv.w, S[4 * r + 3], os[3]);
         }
+        float kt = (ks[0] + ks[1]) + (ks[2] + ks[3]), qt = (os[0] + os[1]) + (os[2] + os[3]);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 1); qt += __shfl_xor_sync(0xffffffffu, qt, 1);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 2); qt += __shfl_xor_sync(0xffffffffu, qt, 2);
+        kt += __shfl_xor_sync(0xffffffffu, kt, 4); qt += __shfl_xor_sync(0xffffffffu, qt, 4);
+        const float u = c2 * (v - c1 * kt);
+#pragma unroll
+        for (int r = 0; r < RPT / 4; ++r) {
+          S[4 * r] = fmaf(kv[r].x, u, c1 * S[4 * r]); S[4 * r + 1] = fmaf(kv[r].y, u, c1 * S[4 * r + 1]);
+          S[4 * r + 2] = fmaf(kv[r].z, u, c1 * S[4 * r + 2]); S[4 * r + 3] = fmaf(kv[r].w, u, c1 * S[4 * r + 3]);
+        }
+        if (live && sub == 0) reinterpret_cast<float*>(o.C)[(size_t)(t0 + tt) * o.ldc + (size_t)h * dv + col] = fmaf(u, cf[tt * 4 + 2], c1 * qt);
+        continue;
       } else {
         const float dx = c2 * v;
 #pragma unroll

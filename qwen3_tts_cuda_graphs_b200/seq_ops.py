@@ -260,7 +260,7 @@ class StepBuilder:
     # ---- recurrences with a matrix state per head -----------------------------------------------------
     def _mstate(self, mode: int, rows: torch.Tensor, raw: torch.Tensor, H: int, G: int, dk: int, dv: int, kcol: int, vcol: int,
                 decay_col: int, write_col: int, w: dict, state: str, y: torch.Tensor):
-        wcols = 2 * H + (2 * G * dk if mode == 0 else 0)
+        wcols = -(-(2 * H + (2 * G * dk + G if mode == 0 else 0)) // 4) * 4      # rows padded to 16 bytes
         ws = self.buf("ms.ws", self.M, wcols)
         kw = dict(M=self.M, N=H * dv, taps=mode, i0=H, i1=G, i2=dk, cin=dv, K=kcol, a_rows=vcol, A=rows, lda=rows.shape[1], res=raw,
                   ldr=raw.shape[1], col_mod=decay_col, m_begin=write_col, scale=w["A_log"], bias=w["dt_bias"],
