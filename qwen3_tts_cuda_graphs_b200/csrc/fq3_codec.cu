@@ -1256,7 +1256,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
         return fail("mstate_scan: bad configuration");
       if (o.taps != 0 && o.taps != 1) return fail("mstate_scan: taps selects the delta rule (0) or the state-space scan (1)");
       if (o.ws_bytes < (int64_t)o.M * mstate_ws_cols(o.i0, o.i1, o.i2, o.taps == 0) * 4) return fail("mstate_scan: workspace too small");
-      if (o.i2 > 256) return fail("mstate_scan: at most 256 state rows per head");
+      if (o.i2 > 512) return fail("mstate_scan: at most 512 state rows per head");
       fq3s_mstate_prep_kernel<<<o.M, 128, 0, s>>>(o);
       count_launches(1);
       dim3 grid((o.cin + MS_COLS - 1) / MS_COLS, o.i0);
@@ -1265,12 +1265,14 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       cudaGetDevice(&dev);
       if (dev >= 0 && dev < 64 && !sattr[dev]) {
         cudaFuncSetAttribute(fq3s_mstate_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(fq3s_mstate_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         sattr[dev] = true;
       }
       if (o.i2 <= 32) fq3s_mstate_scan_kernel<4><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(4), s>>>(o);
       else if (o.i2 <= 64) fq3s_mstate_scan_kernel<8><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(8), s>>>(o);
       else if (o.i2 <= 128) fq3s_mstate_scan_kernel<16><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(16), s>>>(o);
-      else fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o);
+      else if (o.i2 <= 256) fq3s_mstate_scan_kernel<32><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(32), s>>>(o);
+      else fq3s_mstate_scan_kernel<64><<<grid, 128, sizeof(float) * 2 * mstate_buf_floats(64), s>>>(o);
       return 0;
     }
     default: return 1;

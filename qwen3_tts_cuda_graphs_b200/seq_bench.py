@@ -54,8 +54,8 @@ def sizes():
         return SidalornConfig(vocab, width, 1e-5, 4, 3, tuple(layers))
 
     def redodra(width, heads, kv, window, ssm_heads, ssm_vdim, ff, order, vocab=3072):
-        att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, 30.0, 64, 50000.0, sink=True, gate=True)
-        left = SoftmaxAttentionConfig(heads // 2, max(1, kv // 2), 128, 128, 128 ** -0.5, 30.0, window=window, keep_first=4, bias=True, distance=True)
+        att = SoftmaxAttentionConfig(heads, kv, 128, 128, 128 ** -0.5, 50.0, 32, 10000.0, sink=True, gate=True)
+        left = SoftmaxAttentionConfig(heads // 2, max(1, kv // 2), 128, 128, 128 ** -0.5, 50.0, window=window, keep_first=4, bias=True, distance=True)
         mix = {"delta": DeltaRuleConfig(heads // 2, heads // 4, 128, 128, 4), "attention": att,
                "parallel": ParallelMixerConfig(left, StateSpaceConfig(ssm_heads, ssm_vdim, 128, 2, 4, 2))}
         layers, lender = [], None

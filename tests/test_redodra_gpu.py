@@ -169,7 +169,7 @@ ATTN_CASES = {
     "window_edges_peaky": ("left", 4, 2, 8, 6, 24, 90, [7, 2, 31, 30], 5.0, dict(softcap=6.0, mask=(5, 2))),
     "window_of_one": ("left", 2, 1, 4, 4, 16, 40, [3, 20], 3.0, dict(mask=(1, 3))),
     "window_wider_than_the_sequence": ("left", 2, 2, 4, 6, 16, 40, [40], 3.0, dict(mask=(64, 0))),
-    "many_tiles_and_splits": ("attention", 8, 2, 64, 32, 64, 330, [300, 2, 17], 3.0, dict(softcap=30.0, rot=(16, 5000.0))),
+    "many_tiles_and_splits": ("attention", 8, 2, 64, 32, 64, 330, [300, 2, 17], 3.0, dict(softcap=28.0, rot=(16, 5000.0))),
     "long_window_many_tiles": ("left", 4, 4, 16, 16, 32, 300, [129, 150], 4.0, dict(softcap=10.0, mask=(70, 5))),
 }
 
@@ -232,7 +232,7 @@ def test_borrowed_cache_reads_the_lending_layers_rotated_keys():
     assert close_enough(torch.cat(got1), want1, True) and close_enough(torch.cat(got2), want2, True)
 
 
-DELTA_SHAPES = [(3, 3, 5, 7, 2), (4, 2, 32, 40, 4), (2, 1, 130, 16, 1), (1, 1, 64, 64, 3)]
+DELTA_SHAPES = [(3, 3, 5, 7, 2), (4, 2, 32, 40, 4), (2, 1, 130, 16, 1), (1, 1, 64, 64, 3), (1, 1, 300, 8, 2)]
 
 
 @pytest.mark.parametrize("f32", [True, False])
