@@ -122,3 +122,43 @@ def test_command_lines_accept_the_model():
 
     a = build_parser().parse_args(["lm", "--model", "m", "--tokens", "1 2 3", "--greedy", "--prefill-chunk", "7"])
     assert a.fn.__name__ == "cmd_lm" and a.prefill_chunk == 7
+
+
+def test_peaky_weights_put_the_mass_on_single_keys_far_back():
+    """The premise of the GPU test of far keys: with the query projections scaled up, a full-attention row concentrates on
+    single keys, many of them far back, and the windowed rows reach their window's far edge and the kept first positions."""
+    cfg = cases.config(64, 64, [
+        cases.layer(cases.attn(4, 2, 16, 16, 0.25, softcap=25.0, rot=(8, 2000.0)), cases.dense(64)),
+        cases.layer(cases.parallel(cases.attn_mixer(4, 2, 16, 8, 0.25, softcap=25.0, mask=(37, 3)), cases.ssm(4, 8, 16, 2, 3, 2)), cases.dense(32)),
+    ])
+    W = {k: v.to(F64) for k, v in cases.weights(cfg, seed=9, peaky=20.0, sink=8.0).items()}
+    T = 300
+    toks = cases.tokens(cfg, T)
+    h = ro.dyt_norm(W["embed"][torch.tensor(toks)], W, "l0.norm1")
+    q = ro.rotate_interleaved((h @ W["l0.mix.q"].T).reshape(T, 4, 16), 8, 2000.0)
+    k = ro.rotate_interleaved((h @ W["l0.mix.k"].T).reshape(T, 2, 16), 8, 2000.0)
+    top, dist = [], []
+    for i in range(200, T):
+        for hd in range(4):
+            s = (k[: i + 1, hd // 2] @ q[i, hd]) * 0.25
+            s = 25.0 * torch.tanh(s / 25.0)
+            p = torch.softmax(s, 0)                      # among the keys (the sink only scales the row)
+            top.append(float(p.max()))
+            dist.append(i - int(p.argmax()))
+    assert sum(top) / len(top) > 0.3 and max(dist) > 150 and sum(d > 50 for d in dist) > len(dist) // 4
+    # windowed layer: rows whose heaviest key is the window's last visible position or a kept one do occur
+    taps = []
+    ro.forward(cfg, {k_: v for k_, v in W.items()}, toks, taps)
+    h1 = ro.dyt_norm(taps[0], W, "l1.norm1")
+    p_ = "l1.mix.left."
+    q1 = (h1 @ W[p_ + "q"].T + W[p_ + "q.b"]).reshape(T, 4, 16)
+    k1 = (h1 @ W[p_ + "k"].T + W[p_ + "k.b"]).reshape(T, 2, 16)
+    edge = kept = 0
+    for i in range(60, T):
+        for hd in range(4):
+            js = torch.tensor([j for j in range(i + 1) if i - j < 37 or j < 3])
+            s = 25.0 * torch.tanh((k1[js, hd // 2] @ q1[i, hd]) * 0.25 / 25.0) - W[p_ + "r1"][hd] * torch.log1p(W[p_ + "r2"][hd] * (i - js).to(F64))
+            j = int(js[int(s.argmax())])
+            edge += int(i - j >= 33)
+            kept += int(j < 3)
+    assert edge > 10 and kept > 10

@@ -322,7 +322,7 @@ def test_far_keys_window_edges_kept_positions_and_sinks(f32):
         cases.layer(cases.parallel(cases.attn_mixer(4, 2, 16, 8, 0.25, softcap=25.0, mask=(37, 3)), cases.ssm(4, 8, 16, 2, 3, 2)), cases.dense(32)),
         cases.layer(cases.attn(4, 2, 16, 16, 0.25, softcap=25.0, rot=(8, 2000.0), kv_from=0), None),
     ])
-    W = cases.weights(cfg, seed=9, peaky=6.0, sink=3.0)
+    W = cases.weights(cfg, seed=9, peaky=20.0 if f32 else 6.0, sink=8.0 if f32 else 3.0)      # bf16 products: milder peaks, fewer near-ties
     T = 330
     toks = cases.tokens(cfg, T)
     want = ro.forward(cfg, W, toks)
