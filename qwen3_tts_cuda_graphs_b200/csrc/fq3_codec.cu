@@ -1209,7 +1209,11 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
       // bf16 cache and a prompt portion: the tensor-core kernel (FQ3S_ATTN_MMA=0: CUDA cores everywhere)
       static int use_mma = -1;
       if (use_mma < 0) { const char* e7 = getenv("FQ3S_ATTN_MMA"); use_mma = (e7 == nullptr || atoi(e7) != 0) ? 1 : 0; }
-      if (use_mma && !(o.flags & FQ3C_F32) && o.M > 8 && (HG == 1 || HG == 2 || HG == 4 || HG == 8 || HG == 16) && o.i2 % 16 == 0 && o.i2 <= 256 &&
+      // rows per block: a multiple of 16 (one MMA tile per warp) that whole queries fill, i.e. that the group size divides
+      int mma_rows = 0;
+      for (const int w : {4, 8, 3, 6, 5, 7, 2, 1})
+        if (!mma_rows && (16 * w) % HG == 0) mma_rows = 16 * w;
+      if (use_mma && mma_rows && !(o.flags & FQ3C_F32) && o.M > 8 && o.i2 % 16 == 0 && o.i2 <= 256 &&
           o.cin % 16 == 0 && o.cin <= 128 && o.ldr % 8 == 0 && o.taps % 8 == 0 && !(reinterpret_cast<uintptr_t>(o.B) & 15) &&
           !(reinterpret_cast<uintptr_t>(o.p1) & 15) && (o.ldc % 2 == 0 || (o.flags & FQ3C_OUT_F32))) {
         static bool mattr[64] = {};
@@ -1221,7 +1225,7 @@ int seq_run(const fq3c_op& o, cudaStream_t s) {
           cudaFuncSetAttribute(fq3s_cache_attn_mma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
           mattr[dev] = true;
         }
-        const int ROWS = (o.M * HG >= 8192 && cache_attn_mma_smem(128, o.i2, o.cin) <= 110 * 1024) ? 128 : 64, QBLK = ROWS / HG;
+        const int ROWS = (mma_rows == 64 && o.M * HG >= 8192 && cache_attn_mma_smem(128, o.i2, o.cin) <= 110 * 1024) ? 128 : mma_rows, QBLK = ROWS / HG;
         dim3 grid((o.M + QBLK - 1) / QBLK, o.i1);
         const size_t smem = cache_attn_mma_smem(ROWS, o.i2, o.cin);
         if (o.cin <= 32) fq3s_cache_attn_mma_kernel<4><<<grid, ROWS * 2, smem, s>>>(o, ROWS);

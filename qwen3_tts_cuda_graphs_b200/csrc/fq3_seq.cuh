@@ -1427,7 +1427,7 @@ __global__ void __launch_bounds__(128) fq3s_cache_attn_merge_kernel(const fq3c_o
 // ---------------------------------------------------------------------------------------------------------------------------
 // The same attention on the tensor cores for bf16 caches and many queries (prompt portions).  The rows of an MMA tile are
 // (query, head of the group) pairs: a block takes 64 / HG consecutive queries x the HG query heads of one key / value head = 64
-// rows (128 for long portions), 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
+// rows (128 for long portions; another multiple of 16 when HG does not divide 64), 16 per warp, which score the same staged key tile.  Key and value tiles of 64 positions arrive by cp.async into two
 // buffers (one is read while the next arrives); tiles outside every window of the block and beyond the kept first positions are
 // never fetched.  S [16 x 64] = Q K^T (m16n8k16, keys row-major as the B operand), then scale / cap / distance penalty / mask and
 // the online softmax in f32 (fast exponential, logarithm and reciprocal: errors around 1e-6), then O [16 x dv] += P V with every weight as a bf16 pair p_hi + p_lo (two MMAs: 16 mantissa bits)

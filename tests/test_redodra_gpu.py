@@ -170,6 +170,8 @@ ATTN_CASES = {
     "window_of_one": ("left", 2, 1, 4, 4, 16, 40, [3, 20], 3.0, dict(mask=(1, 3))),
     "window_wider_than_the_sequence": ("left", 2, 2, 4, 6, 16, 40, [40], 3.0, dict(mask=(64, 0))),
     "many_tiles_and_splits": ("attention", 8, 2, 64, 32, 64, 330, [300, 2, 17], 3.0, dict(softcap=28.0, rot=(16, 5000.0))),
+    "three_and_six_heads_per_key_head": ("attention", 6, 2, 32, 16, 48, 200, [150, 2, 33], 3.0, dict(softcap=12.0, rot=(32, 3000.0))),
+    "six_heads_one_key_head_window": ("left", 6, 1, 16, 32, 32, 160, [100, 47], 4.0, dict(mask=(50, 2))),
     "long_window_many_tiles": ("left", 4, 4, 16, 16, 32, 300, [129, 150], 4.0, dict(softcap=10.0, mask=(70, 5))),
 }
 
